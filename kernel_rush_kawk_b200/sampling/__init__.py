@@ -1,0 +1,5 @@
+"""Greedy and temperature token selection."""
+
+from .sampler import Sampler, SamplingParams
+
+__all__ = ["Sampler", "SamplingParams"]
