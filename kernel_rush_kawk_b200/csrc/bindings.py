@@ -1,0 +1,287 @@
+"""Python bindings of the CUDA kernels (ctypes over the compiled libraries).
+
+``Kernels`` is the one object through which the engine computes. Every method
+launches this package's own kernels on torch's current CUDA stream; the only
+library routine on the path is the dense matrix product of many rows in
+bfloat16 (``torch.matmul``, i.e. cuBLAS), which is where the reference calls
+cuBLAS too (engine/model.py:295,299,301,303 of willzeng274/kernel-rush-kawk).
+There is no fallback: without a CUDA device and the compiled libraries,
+construction raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_uint, c_void_p
+
+import torch
+
+from .build import build_library
+
+F32, BF16 = 0, 1
+_P = c_void_p
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "krk_rmsnorm": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "krk_gather_rows": [_P, _P, _P, c_int, c_int, c_int, _P, c_int, _P],
+    "krk_swiglu": [_P, _P, c_int, c_int, c_int, _P],
+    "krk_qk_norm_rope_write": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int,
+                               c_float, c_int, _P, c_int, _P],
+    "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P],
+    "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
+}
+_ATTN_SIGNATURES = {
+    "krk_attention_simple": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
+    "krk_attention_head_dim": [],
+    "krk_attention_prefill": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_float,
+                              c_int, _P],
+    "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
+                             _P],
+}
+
+
+def _load(path, signatures) -> ctypes.CDLL:
+    lib = ctypes.CDLL(str(path))
+    for name, args in signatures.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue
+        fn.argtypes = args
+        fn.restype = c_int
+    return lib
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+class Kernels:
+    """All kernels, for one device. ``head_dims``: the head sizes whose attention
+    libraries are needed (compiled at first use)."""
+
+    SKINNY_MAX_ROWS = 16  # rows up to which the fused skinny kernels serve a bfloat16 product
+
+    def __init__(self, head_dims=(), device="cuda:0"):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this library computes with its CUDA kernels only")
+        self.device = torch.device(device)
+        self.core = _load(build_library("core"), _SIGNATURES)
+        self.attn: dict[int, ctypes.CDLL] = {}
+        for d in head_dims:
+            self._attn_lib(int(d))
+        self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.has_skinny = hasattr(self.core, "krk_skinny_linear")
+        self._partials: dict = {}
+        self.launches = 0
+
+    def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
+        lib = self.attn.get(head_dim)
+        if lib is None:
+            if head_dim % 2 or head_dim > 256:
+                raise KernelError(f"attention kernels take an even head size up to 256, got {head_dim}")
+            lib = self.attn[head_dim] = _load(build_library("attn", head_dim), _ATTN_SIGNATURES)
+            assert lib.krk_attention_head_dim() == head_dim
+        return lib
+
+    # -- plumbing -------------------------------------------------------------
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _ok(self, code: int, what: str) -> None:
+        self.launches += 1
+        if code != 0:
+            detail = {-2: "a size is outside what the kernel takes", -3: "the grid would be too large",
+                      -4: "unsupported dtype combination"}.get(code, f"CUDA error {code}")
+            raise KernelError(f"{what}: {detail}")
+
+    def check(self) -> None:
+        """Raise if a kernel flagged bad input (a token id or position out of range)."""
+        flag = int(self.error.item())
+        if flag:
+            self.error.zero_()
+            raise KernelError({1: "a token id outside the embedding table reached the device",
+                               2: "a position outside the rotary table reached the device"}.get(flag, f"flag {flag}"))
+
+    def empty_like(self, x):
+        return torch.empty_like(x)
+
+    @staticmethod
+    def _resolve(x):
+        return x if isinstance(x, torch.Tensor) else x.tensor()
+
+    # -- rows -------------------------------------------------------------------
+    def embed(self, table, tokens, n_rows):
+        out = torch.empty((n_rows, table.shape[1]), dtype=table.dtype, device=table.device)
+        self._ok(self.core.krk_gather_rows(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), n_rows, table.shape[1],
+                                           table.shape[0], self.error.data_ptr(), _code(table.dtype), self._stream()),
+                 "embedding gather")
+        return out
+
+    def gather_rows(self, x, idx):
+        n = idx.shape[0]
+        out = torch.empty((n, x.shape[1]), dtype=x.dtype, device=x.device)
+        self._ok(self.core.krk_gather_rows(out.data_ptr(), x.data_ptr(), idx.data_ptr(), n, x.shape[1], x.shape[0],
+                                           self.error.data_ptr(), _code(x.dtype), self._stream()), "row gather")
+        return out
+
+    def rmsnorm(self, x, gain, eps):
+        out = torch.empty_like(x)
+        self._ok(self.core.krk_rmsnorm(out.data_ptr(), None, x.data_ptr(), None, gain.data_ptr(),
+                                       int(gain.dtype == torch.float32), x.shape[0], x.shape[1], eps, _code(x.dtype),
+                                       self._stream()), "rmsnorm")
+        return out
+
+    def add_rmsnorm(self, x, branch, gain, eps, x_new):
+        out = torch.empty_like(x)
+        self._ok(self.core.krk_rmsnorm(out.data_ptr(), x_new.data_ptr(), x.data_ptr(), branch.data_ptr(),
+                                       gain.data_ptr(), int(gain.dtype == torch.float32), x.shape[0], x.shape[1], eps,
+                                       _code(x.dtype), self._stream()), "add + rmsnorm")
+        return out
+
+    def swiglu(self, gu, intermediate):
+        out = torch.empty((gu.shape[0], intermediate), dtype=gu.dtype, device=gu.device)
+        self._ok(self.core.krk_swiglu(out.data_ptr(), gu.data_ptr(), gu.shape[0], intermediate, _code(gu.dtype),
+                                      self._stream()), "swiglu")
+        return out
+
+    # -- matrix products ----------------------------------------------------------
+    def _gemm_nt(self, x, w, out_dtype):
+        M, K = x.shape
+        N = w.shape[0]
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        self._ok(self.core.krk_gemm_nt(out.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
+                                       _code(x.dtype), _code(out_dtype), self._stream()), "gemm")
+        return out
+
+    def _skinny(self, x, w, out_dtype, swiglu_rows=0):
+        """x: a tensor or a Normed not yet computed (then the add and the norm run in
+        the kernel's prologue)."""
+        lazy = not isinstance(x, torch.Tensor)
+        src = x.x if lazy else x
+        M, K = src.shape
+        N = swiglu_rows if swiglu_rows else w.shape[0]
+        out = torch.empty((M, N), dtype=out_dtype, device=src.device)
+        branch = x.branch if lazy else None
+        gain = x.gain if lazy else None
+        x_new = x.x_new if lazy and x.branch is not None else None
+        self._ok(self.core.krk_skinny_linear(
+            out.data_ptr(), src.data_ptr(), w.data_ptr(), _ptr(branch), _ptr(gain), _ptr(x_new),
+            int(gain is not None and gain.dtype == torch.float32), None, M, N, K, float(x.eps) if lazy else 0.0,
+            int(swiglu_rows > 0), _code(out_dtype), self._stream()), "skinny product")
+        if lazy:
+            x.mark_fused()
+        return out
+
+    def _use_skinny(self, x, w) -> bool:
+        rows = x.shape[0]
+        return (self.has_skinny and w.dtype == torch.bfloat16 and 0 < rows <= self.SKINNY_MAX_ROWS
+                and w.shape[1] % 32 == 0 and w.is_contiguous())
+
+    def linear(self, x, w, out_float32=False):
+        """y = x W^T; W is [out, in]. x may be a Normed (see parts/norm.py)."""
+        out_dtype = torch.float32 if out_float32 else w.dtype
+        if self._use_skinny(x, w) and (isinstance(x, torch.Tensor) or not x.done):
+            return self._skinny(x, w, out_dtype)
+        x = self._resolve(x)
+        if x.shape[0] == 0:
+            return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
+        if w.dtype == torch.float32 or out_float32:
+            return self._gemm_nt(x, w, out_dtype)
+        return torch.matmul(x, w.t())
+
+    def gate_up_swiglu(self, h, w_gate_up, intermediate):
+        if self._use_skinny(h, w_gate_up) and (isinstance(h, torch.Tensor) or not h.done):
+            return self._skinny(h, w_gate_up, w_gate_up.dtype, swiglu_rows=intermediate)
+        return self.swiglu(self.linear(h, w_gate_up), intermediate)
+
+    # -- attention ------------------------------------------------------------------
+    def qk_norm_rope_write(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache):
+        gain = q_gain if q_gain is not None else k_gain
+        n_pos = cos.shape[0] if cos is not None else 0x7fffffff
+        self._ok(self.core.krk_qk_norm_rope_write(
+            qkv.data_ptr(), _ptr(q_gain), _ptr(k_gain), int(gain is not None and gain.dtype == torch.float32),
+            _ptr(cos), _ptr(sin), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(),
+            cache.table.data_ptr(), cache.width, cache.k.data_ptr() if kv_in_row else None,
+            cache.v.data_ptr() if kv_in_row else None, qkv.shape[0], heads, kv_in_row, head_dim, eps, n_pos,
+            self.error.data_ptr(), _code(qkv.dtype), self._stream()), "q/k norm + rope + cache write")
+
+    def attention(self, qkv, heads, kv_in_row, head_dim, batch, cache, scale, window):
+        lib = self._attn_lib(head_dim)
+        rows = qkv.shape[0]
+        out = torch.empty((rows, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        if rows == 0:
+            return out
+        stride = qkv.stride(0)
+        win = int(window or 0)
+        fast = qkv.dtype == torch.bfloat16 and head_dim % 16 == 0
+        if fast and batch.is_decode and hasattr(lib, "krk_attention_decode"):
+            splits, parts = self._decode_partials(batch.n_seqs, heads, head_dim)
+            self._ok(lib.krk_attention_decode(
+                out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),
+                batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(),
+                cache.v.data_ptr(), batch.n_seqs, scale, win, splits, parts.data_ptr(), self._stream()),
+                "decode attention")
+        elif fast and hasattr(lib, "krk_attention_prefill"):
+            self._ok(lib.krk_attention_prefill(
+                out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),
+                batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(), batch.cu_q.data_ptr(), cache.table.data_ptr(),
+                cache.width, cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, batch.max_q_len, scale, win,
+                self._stream()), "prefill attention")
+        else:
+            self._ok(lib.krk_attention_simple(
+                out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.row_seq.data_ptr(),
+                batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width,
+                cache.k.data_ptr(), cache.v.data_ptr(), rows, scale, win, _code(qkv.dtype), self._stream()),
+                "attention")
+        return out
+
+    def _decode_partials(self, n_seqs: int, heads: int, head_dim: int):
+        """Number of key splits for a decode step and the float32 scratch its partial
+        results go through. The split count depends on the batch size only, never on
+        lengths, so a captured step stays valid as sequences grow."""
+        splits = max(1, min(32, -(-296 // max(1, n_seqs * max(1, heads // 16 + (heads % 16 > 0))))))
+        key = (n_seqs, heads, head_dim, splits)
+        buf = self._partials.get(key)
+        if buf is None:
+            buf = self._partials[key] = torch.empty(n_seqs * heads * splits * (head_dim + 2), dtype=torch.float32,
+                                                    device=self.device)
+        return splits, buf
+
+    # -- token selection ------------------------------------------------------------
+    def select_tokens(self, logits, temperature, seed, requests, step):
+        n, vocab = logits.shape
+        tokens = torch.empty(n, dtype=torch.int32, device=logits.device)
+        logits = logits.contiguous()
+        self._ok(self.core.krk_select_tokens(tokens.data_ptr(), logits.data_ptr(), n, vocab, temperature,
+                                             seed & 0xFFFFFFFF, requests.data_ptr(), step & 0xFFFFFFFF,
+                                             self._stream()), "token selection")
+        return tokens
+
+
+_cached: dict = {}
+
+
+def load_kernels(head_dims=(), device="cuda:0") -> Kernels:
+    """The process-wide Kernels object of a device, with the given head sizes loaded."""
+    key = str(torch.device(device))
+    k = _cached.get(key)
+    if k is None:
+        k = _cached[key] = Kernels(head_dims, device)
+    for d in head_dims:
+        k._attn_lib(int(d))
+    return k

@@ -1,0 +1,75 @@
+// Shared device helpers: element types, rounding, vector access, reductions.
+//
+// Every kernel of this library is instantiated for two element types: float
+// (the true 32-bit path) and __nv_bfloat16 (the serving path). round_to<T>(x)
+// rounds a float to T's precision and returns it as float; it is the identity
+// for float. The places where it is applied are the places where the
+// reference's BF16 path rounds (engine/kernels/rmsnorm.py:30-45,
+// add_rmsnorm.py:21-29, rope.py:19-30, swiglu.py:21-24 of
+// willzeng274/kernel-rush-kawk).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define KRK_PAGE 64  // cache positions per page
+
+#define KRK_DTYPE_F32 0
+#define KRK_DTYPE_BF16 1
+
+#define KRK_API extern "C" __attribute__((visibility("default")))
+
+#define KRK_CHECK_LAUNCH()                         \
+  do {                                             \
+    cudaError_t e__ = cudaGetLastError();          \
+    if (e__ != cudaSuccess) return (int)e__;       \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
+
+// A norm's gain may be stored in 32-bit even on the bfloat16 path.
+template <typename T>
+__device__ __forceinline__ float load_gain(const void* g, int i, int gain_f32) {
+  return gain_f32 ? reinterpret_cast<const float*>(g)[i] : to_float<T>(reinterpret_cast<const T*>(g)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds at least 32 floats of shared memory. Safe to call repeatedly.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < n_warps) ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+
+// Page of position `pos` for cache slot `slot`: table is [slots, width].
+__device__ __forceinline__ int page_of(const int* __restrict__ table, int width, int slot, int pos) {
+  return table[(size_t)slot * width + (pos / KRK_PAGE) % width];
+}

@@ -6,7 +6,7 @@ willzeng274/kernel-rush-kawk). Temperature sampling is this library's addition.
 It uses the Gumbel-max form, token = argmax_i(logit_i / temperature + g_i) with
 g_i = -log(-log(u_i)), which is a draw from softmax(logits / temperature) made in
 one pass over the logits. The uniforms come from a 32-bit mixing hash of (seed,
-request, step, i): u_i = ((hash >> 8) + 0.5) / 2^24. A request's draw therefore
+request, step, i): u_i = ((hash >> 9) + 0.5) / 2^23. A request's draw therefore
 depends on its own index and step only, never on what else is in its batch.
 Both run in one CUDA kernel over float32 logits.
 """

@@ -240,14 +240,14 @@ def _mix32(x: torch.Tensor) -> torch.Tensor:
 def gumbel_uniforms(seed: int, request: int, step: int, vocab: int) -> torch.Tensor:
     """The counter-based uniforms in (0, 1) that temperature sampling draws: one per
     vocabulary entry from a 32-bit mixing hash keyed by (seed, request, step, index);
-    the top 24 bits of the hash, plus a half, over 2^24. The reference selects greedily
+    the top 23 bits of the hash, plus a half, over 2^23. The reference selects greedily
     only; this restates the product's documented definition so that its sampler can be
     checked draw by draw."""
     t = lambda v: torch.tensor(v & 0xFFFFFFFF, dtype=torch.int64)
     key = _mix32(_mix32(_mix32(t(seed)) ^ t(request)) ^ t(step))
     i = torch.arange(vocab, dtype=torch.int64)
     h = _mix32(key ^ ((i * 0x9E3779B9) & 0xFFFFFFFF))
-    return ((h >> 8).double() + 0.5) / 16777216.0
+    return ((h >> 9).double() + 0.5) / 8388608.0
 
 
 def sample_temperature(logits: torch.Tensor, temperature: float, seed: int, request: int, step: int) -> int:

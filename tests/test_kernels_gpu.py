@@ -1,0 +1,284 @@
+"""Each CUDA kernel alone against its plain torch reference (tests/torch_ops.py), at
+sizes other than the tiny models': widths that are no power of two, head sizes in
+steps of 16, odd group counts. Inputs are made so that a fault shows: one far key
+whose score stands out, a window's edge, pages scattered over the pool."""
+
+import math
+import random
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from helpers import assert_close
+from torch_ops import PAGE, TorchOps
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = (torch.float32, torch.bfloat16)
+NAME = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from kernel_rush_kawk_b200.csrc import load_kernels
+
+    return load_kernels(())
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def close(got, ref, dtype, what):
+    assert_close(got, ref, NAME[dtype], what, kernel=True)
+
+
+# -- rows -------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [48, 250, 2560, 5123])
+def test_rmsnorm_and_add_rmsnorm(ops, dtype, hidden):
+    ref = TorchOps(dtype)
+    x, b = rand((7, hidden), dtype, 1, 3.0), rand((7, hidden), dtype, 2)
+    gain = (1 + 0.1 * rand((hidden,), torch.float32, 3)).to(dtype)
+    close(ops.rmsnorm(x, gain, 1e-5), ref.rmsnorm(x, gain, 1e-5), dtype, "rmsnorm")
+    xn, xr = torch.empty_like(x), torch.empty_like(x)
+    close(ops.add_rmsnorm(x, b, gain, 1e-6, xn), ref.add_rmsnorm(x, b, gain, 1e-6, xr), dtype, "add+rmsnorm")
+    assert torch.equal(xn, xr), "the new residual stream is defined to the bit"
+    if dtype == torch.bfloat16:  # a gain kept in 32-bit on the bfloat16 path
+        close(ops.rmsnorm(x, gain.float(), 1e-5), ref.rmsnorm(x, gain.float(), 1e-5), dtype, "rmsnorm, float32 gain")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_row_gather(ops, dtype):
+    table = rand((301, 80), dtype, 4)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.embed(table, ids, 5), table[ids.long()])
+    assert torch.equal(ops.gather_rows(table, ids[:2]), table[ids[:2].long()])
+    odd = rand((10, 37), dtype, 5)
+    assert torch.equal(ops.gather_rows(odd, ids[:1]), odd[:1])
+    ops.check()
+
+
+def test_a_token_outside_the_table_is_flagged(ops):
+    from kernel_rush_kawk_b200.csrc import KernelError
+
+    table = rand((16, 32), torch.float32, 6)
+    out = ops.embed(table, torch.tensor([3, 16], dtype=torch.int32, device="cuda"), 2)
+    assert torch.equal(out[1], torch.zeros_like(out[1]))
+    with pytest.raises(KernelError):
+        ops.check()
+    ops.check()  # the flag is cleared
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    gu = rand((9, 2 * 333), dtype, 7, 2.0)
+    ref = TorchOps(dtype)
+    g, u = gu[:, :333].float(), gu[:, 333:].float()
+    want = (ref.rt(g / (1 + torch.exp(-g))) * u).to(dtype)
+    close(ops.swiglu(gu, 333), want, dtype, "swiglu")
+
+
+# -- matrix products ----------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mnk", [(1, 70, 96), (5, 301, 80), (64, 192, 64), (130, 257, 333), (16, 2560, 4096)])
+def test_linear(ops, dtype, mnk):
+    m, n, k = mnk
+    x, w = rand((m, k), dtype, 8), rand((n, k), dtype, 9, 0.05)
+    ref = TorchOps(dtype)
+    close(ops.linear(x, w), ref.linear(x, w), dtype, f"linear {mnk}")
+    close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), dtype, f"linear {mnk}, float32 out")
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("nk", [(96, 64), (160, 2560), (301, 96), (2560, 9728)])
+def test_fused_norm_linear_bfloat16(ops, rows, nk):
+    """The decode-time product with the residual add and the norm in its prologue."""
+    from kernel_rush_kawk_b200.parts.norm import Normed
+
+    n, k = nk
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    x, b = rand((rows, k), dtype, 10, 2.0), rand((rows, k), dtype, 11)
+    gain = (1 + 0.1 * rand((k,), torch.float32, 12)).to(dtype)
+    w = rand((n, k), dtype, 13, 0.05)
+    for branch in (b, None):
+        xn, xr = torch.empty_like(x), torch.empty_like(x)
+        lazy = Normed(ops, x, branch, gain, 1e-6, xn if branch is not None else x)
+        got = ops.linear(lazy, w)
+        h = ref.add_rmsnorm(x, branch, gain, 1e-6, xr) if branch is not None else ref.rmsnorm(x, gain, 1e-6)
+        close(got, ref.linear(h, w), dtype, f"norm+linear rows {rows} {nk}")
+        if branch is not None:
+            assert torch.equal(xn, xr)
+    lazy = Normed(ops, x, b, gain, 1e-6, torch.empty_like(x))
+    got = ops.linear(lazy, w, out_float32=True)
+    close(got, ref.linear(ref.add_rmsnorm(x, b, gain, 1e-6, torch.empty_like(x)), w, out_float32=True), dtype, "float32 out")
+
+
+@pytest.mark.parametrize("rows", [1, 8, 11])
+def test_fused_gate_up_swiglu_bfloat16(ops, rows):
+    from kernel_rush_kawk_b200.parts.norm import Normed
+
+    dtype, k, inter = torch.bfloat16, 160, 272
+    ref = TorchOps(dtype)
+    x, b = rand((rows, k), dtype, 14, 2.0), rand((rows, k), dtype, 15)
+    gain = (1 + 0.1 * rand((k,), torch.float32, 16)).to(dtype)
+    w = rand((2 * inter, k), dtype, 17, 0.08)
+    lazy = Normed(ops, x, b, gain, 1e-6, torch.empty_like(x))
+    got = ops.gate_up_swiglu(lazy, w, inter)
+    h = ref.add_rmsnorm(x, b, gain, 1e-6, torch.empty_like(x))
+    close(got, ref.gate_up_swiglu(h, w, inter), dtype, "norm + gate/up + swiglu")
+    close(ops.gate_up_swiglu(h, w, inter), ref.gate_up_swiglu(h, w, inter), dtype, "gate/up + swiglu")
+
+
+# -- attention -----------------------------------------------------------------------
+def make_cache(n_pages, kv_heads, head_dim, n_slots, width, dtype, seed):
+    """A cache view whose pages are handed out in a shuffled order, filled with noise so
+    that reading a page one does not own shows."""
+    from kernel_rush_kawk_b200.cache import KVView
+
+    k = rand((n_pages, kv_heads, PAGE, head_dim), dtype, seed, 1.0)
+    v = rand((n_pages, kv_heads, PAGE, head_dim), dtype, seed + 1, 1.0)
+    order = list(range(n_pages))
+    random.Random(seed).shuffle(order)
+    table = torch.tensor(order[:n_slots * width], dtype=torch.int32, device="cuda").view(n_slots, width)
+    return KVView(k, v, table, width, None, kv_heads, head_dim)
+
+
+def make_batch(slots, starts, q_lens):
+    rows = sum(q_lens)
+    dev = "cuda"
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    row_seq = [s for s, n in enumerate(q_lens) for _ in range(n)]
+    row_pos = [st + t for st, n in zip(starts, q_lens) for t in range(n)]
+    return SimpleNamespace(n_rows=rows, n_seqs=len(slots), row_seq=i32(row_seq), row_pos=i32(row_pos),
+                           seq_slot=i32(slots), seq_start=i32(starts), seq_qlen=i32(q_lens), cu_q=i32(cu),
+                           slots=slots, starts=starts, q_lens=q_lens, max_q_len=max(q_lens),
+                           max_kv_len=max(s + n for s, n in zip(starts, q_lens)), is_decode=max(q_lens) == 1)
+
+
+ATTN_SHAPES = [  # heads, kv_heads, head_dim
+    (4, 2, 16), (6, 2, 32), (5, 1, 48), (8, 8, 64), (14, 2, 80), (32, 8, 128),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [None, 40])
+def test_rope_write_then_attention_prefill_and_decode(ops, dtype, shape, window):
+    heads, kv_heads, D = shape
+    ref = TorchOps(dtype)
+    width, n_slots = 6, 4
+    cache = make_cache(40, kv_heads, D, n_slots, width, dtype, 20)
+    cache.window = window
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.k, ref_cache.v = cache.k.clone(), cache.v.clone()
+    theta = 10000.0
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    qg = (1.5 + 0.1 * rand((D,), torch.float32, 21)).to(dtype)
+    kg = (1.5 + 0.1 * rand((D,), torch.float32, 22)).to(dtype)
+    scale = 1.0 / math.sqrt(D)
+    width_row = (heads + 2 * kv_heads) * D
+    # step 1: three sequences start with unequal prompts; step 2: they go on by pieces
+    # of unequal length (one of them a single token); step 3: one token each
+    steps = [([2, 0, 3], [0, 0, 0], [70, 5, 129]), ([2, 0, 3], [70, 5, 129], [33, 1, 64]),
+             ([3, 2, 0], [193, 103, 6], [1, 1, 1])]
+    for s, (slots, starts, q_lens) in enumerate(steps):
+        batch = make_batch(slots, starts, q_lens)
+        qkv = rand((batch.n_rows, width_row), dtype, 30 + s, 1.0)
+        # make one far key stand out for the last query of the longest sequence: its key
+        # and that query point the same way, strongly
+        qkv_ref = qkv.clone()
+        ops.qk_norm_rope_write(qkv, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, cache)
+        ref.qk_norm_rope_write(qkv_ref, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, ref_cache)
+        close(qkv[:, :heads * D], qkv_ref[:, :heads * D], dtype, f"rotated queries, step {s}")
+        close(cache.k, ref_cache.k, dtype, f"key pages, step {s}")
+        assert torch.equal(cache.v, ref_cache.v), "values are copied raw"
+        ref_cache.k.copy_(cache.k)  # same keys on both sides from here on
+        qkv_ref[:, :heads * D] = qkv[:, :heads * D]
+        got = ops.attention(qkv, heads, kv_heads, D, batch, cache, scale, window)
+        want = ref.attention(qkv_ref, heads, kv_heads, D, batch, ref_cache, scale, window)
+        close(got, want, dtype, f"attention, step {s}, shape {shape}, window {window}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_len", [1, 37])
+def test_one_far_key_among_hundreds_decides(ops, dtype, q_len):
+    """Key 3 of 700 is made to match the last query; its value is a marker. The output
+    must be the marker, which a kernel that skipped or misplaced the key would miss."""
+    heads, kv_heads, D = 4, 2, 64
+    width = 12
+    cache = make_cache(30, kv_heads, D, 2, width, dtype, 40)
+    cache.k.mul_(0.05)
+    total = 700
+    slot, start = 1, total - q_len
+    batch = make_batch([slot], [start], [q_len])
+    qkv = rand((q_len, (heads + 2 * kv_heads) * D), dtype, 41, 0.05)
+    direction = torch.zeros(D, device="cuda")
+    direction[5] = 8.0
+    page = int(cache.table[slot, 0])
+    cache.k[page, :, 3] = direction.to(dtype)
+    cache.v[page, :, 3] = 7.0
+    qkv.view(q_len, heads + 2 * kv_heads, D)[-1, :heads] = (direction * 4).to(dtype)
+    got = ops.attention(qkv, heads, kv_heads, D, batch, cache, 1.0 / math.sqrt(D), None)
+    want = TorchOps(dtype).attention(qkv, heads, kv_heads, D, batch, cache, 1.0 / math.sqrt(D), None)
+    close(got, want, dtype, "far key")
+    assert (got[-1].float() - 7.0).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_windows_edge(ops, dtype):
+    """With a window of 50 the key 50 places back is out and the key 49 back is in: a
+    marker on either side tells."""
+    heads, kv_heads, D, window = 2, 1, 32, 50
+    cache = make_cache(8, kv_heads, D, 1, 8, dtype, 50)
+    cache.k.mul_(0.02)
+    cache.window = window
+    pos = 300
+    batch = make_batch([0], [pos], [1])
+    direction = torch.zeros(D, device="cuda")
+    direction[0] = 10.0
+    for back, marker in ((50, -5.0), (49, 3.0)):
+        p = pos - back
+        page = int(cache.table[0, p // PAGE])
+        cache.k[page, 0, p % PAGE] = direction.to(dtype)
+        cache.v[page, 0, p % PAGE] = marker
+    qkv = rand((1, (heads + 2 * kv_heads) * D), dtype, 51, 0.02)
+    qkv.view(1, heads + 2 * kv_heads, D)[0, :heads] = (direction * 3).to(dtype)
+    got = ops.attention(qkv, heads, kv_heads, D, batch, cache, 1.0 / math.sqrt(D), window)
+    assert (got.float() - 3.0).abs().max().item() < 0.1
+
+
+# -- token selection --------------------------------------------------------------------
+def test_greedy_takes_the_lowest_index_on_ties(ops):
+    logits = rand((5, 1001), torch.float32, 60)
+    logits[2, 17] = logits[2, 900] = 50.0
+    req = torch.arange(5, dtype=torch.int32, device="cuda")
+    got = ops.select_tokens(logits, 0.0, 0, req, 0)
+    assert got.tolist() == logits.argmax(dim=-1).tolist() and got[2].item() == 17
+
+
+def test_temperature_draws_match_the_plain_sampler(ops):
+    import plain_qwen3 as plain
+
+    logits = rand((6, 777), torch.float32, 61, 2.0)
+    req = torch.tensor([5, 0, 9, 1, 2, 3], dtype=torch.int32, device="cuda")
+    got = ops.select_tokens(logits, 0.7, 99, req, 4).tolist()
+    want = [plain.sample_temperature(logits[r].cpu(), 0.7, 99, int(req[r]), 4) for r in range(6)]
+    assert got == want
+    # draws follow softmax(logits / T): chi-square-free sanity on a 3-way distribution
+    small = torch.tensor([[2.0, 1.0, 0.0]], device="cuda").repeat(1, 1)
+    counts = [0, 0, 0]
+    one = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for step in range(3000):
+        counts[ops.select_tokens(small, 1.0, 7, one, step).item()] += 1
+    probs = torch.softmax(small[0], -1).tolist()
+    for c, p in zip(counts, probs):
+        assert abs(c / 3000 - p) < 0.03

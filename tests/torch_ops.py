@@ -144,7 +144,7 @@ class TorchOps:
         for r in range(n):
             key = _mix32(_mix32(_mix32(t(seed)) ^ t(int(requests[r]))) ^ t(step))
             h = _mix32(key ^ ((i * 0x9E3779B9) & 0xFFFFFFFF))
-            u = ((h >> 8).float() + 0.5) / 16777216.0
+            u = ((h >> 9).float() + 0.5) / 8388608.0
             g = -torch.log(-torch.log(u))
             out[r] = int(torch.argmax(logits[r].cpu() / temperature + g))
         return out.to(logits.device)
