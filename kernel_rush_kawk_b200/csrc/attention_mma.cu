@@ -1,0 +1,434 @@
+// Causal grouped-query attention over the paged cache on the tensor cores
+// (mma.sync m16n8k16, bfloat16 in, float32 accumulate): one kernel for steps that
+// bring many tokens per sequence (prefill, chunks), one for single-token steps
+// (decode, split over the keys), and the merge of the splits.
+//
+// Numerics follow the reference's decode kernel (engine/kernels/attention.py:9-11,
+// 104-122 of willzeng274/kernel-rush-kawk): scores and softmax statistics in
+// float32, probabilities rounded to bfloat16 before P.V, output accumulated in
+// float32 and divided by the sum once at the end. A query at position p sees keys
+// max(0, p - window + 1)..p (window 0: from key 0). As there (attention.py:70-73),
+// all G = HQ / HKV query heads of a kv head share one read of K and V: the rows of
+// a tile are (token, group member) pairs, row R -> token R / G, head kh * G + R % G.
+//
+// A key block is one cache page (64 positions), contiguous in memory for one kv
+// head; blocks are brought to shared memory with cp.async, two stages.
+//
+// Compiled once per head size: -DKRK_HEAD_DIM=<D>, D a multiple of 16 up to 256.
+#include "mma.cuh"
+
+#ifndef KRK_HEAD_DIM
+#error "compile with -DKRK_HEAD_DIM=<head size>"
+#endif
+
+#if KRK_HEAD_DIM % 16 == 0 && KRK_HEAD_DIM <= 256
+
+namespace {
+
+constexpr int D = KRK_HEAD_DIM;
+constexpr int DP = D + 8;            // shared-memory row pitch (elements): 16 bytes of padding
+constexpr int KSTEPS = D / 16;       // k-steps of Q.K^T
+constexpr int DTILES = D / 8;        // n-tiles of P.V
+constexpr int THREADS = 128;
+constexpr int TILE_ELEMS = KRK_PAGE * DP;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// Copy one page [64][D] of one kv head to shared memory [64][DP], all threads of the block.
+__device__ __forceinline__ void load_page(bf16* dst, const bf16* __restrict__ src) {
+  constexpr int CHUNKS = KRK_PAGE * (D / 8);
+  for (int i = threadIdx.x; i < CHUNKS; i += THREADS) {
+    const int key = i / (D / 8), ch = i % (D / 8);
+    cp_async_16(dst + key * DP + ch * 8, src + key * D + ch * 8);
+  }
+}
+
+// S[16 x (8*NTILES)] = Q[16 x D] . K^T for keys key0 .. key0 + 8*NTILES - 1 of the tile in shared memory.
+template <int NTILES>
+__device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&qf)[KSTEPS][4], const bf16* ks, int key0,
+                                        int lane) {
+#pragma unroll
+  for (int n = 0; n < NTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+    for (int n = 0; n < NTILES; n += 2) {
+      uint32_t b0, b1, b2, b3;
+      const bf16* p = ks + (key0 + n * 8 + ((lane >> 4) << 3) + (lane & 7)) * DP + kk * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(b0, b1, b2, b3, p);
+      mma_bf16_16816(s[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+      mma_bf16_16816(s[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+    }
+  }
+}
+
+// O[16 x D] += P[16 x (8*NTILES)] . V for the same keys; p holds probabilities (float) in S's layout.
+template <int NTILES>
+__device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[NTILES][4], const bf16* vs, int key0,
+                                        int lane) {
+#pragma unroll
+  for (int kk = 0; kk < NTILES / 2; ++kk) {  // 16 keys per step
+    const uint32_t a0 = pack_bf16x2(p[2 * kk][0], p[2 * kk][1]);
+    const uint32_t a1 = pack_bf16x2(p[2 * kk][2], p[2 * kk][3]);
+    const uint32_t a2 = pack_bf16x2(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+    const uint32_t a3 = pack_bf16x2(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+    for (int n = 0; n < DTILES; n += 2) {
+      uint32_t b0, b1, b2, b3;
+      const bf16* q = vs + (key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + n * 8 + (lane >> 4) * 8;
+      ldmatrix_x4_trans(b0, b1, b2, b3, q);
+      mma_bf16_16816(o[n], a0, a1, a2, a3, b0, b1);
+      mma_bf16_16816(o[n + 1], a0, a1, a2, a3, b2, b3);
+    }
+  }
+}
+
+// Load the A fragments of one 16-row tile of queries; row r of the tile is at qrow[r half] (null: zero row).
+__device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], const bf16* q_lo, const bf16* q_hi, int lane) {
+  const int t = lane & 3;
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    const int d = kk * 16 + 2 * t;
+    qf[kk][0] = q_lo ? *reinterpret_cast<const uint32_t*>(q_lo + d) : 0u;
+    qf[kk][1] = q_hi ? *reinterpret_cast<const uint32_t*>(q_hi + d) : 0u;
+    qf[kk][2] = q_lo ? *reinterpret_cast<const uint32_t*>(q_lo + d + 8) : 0u;
+    qf[kk][3] = q_hi ? *reinterpret_cast<const uint32_t*>(q_hi + d + 8) : 0u;
+  }
+}
+
+// One online-softmax update of a thread's two rows over NTILES*8 keys. s is in log2
+// units already (scaled by scale*log2(e)) and masked with -inf where invisible.
+template <int NTILES>
+__device__ __forceinline__ void softmax_update(float (&s)[NTILES][4], float (&m)[2], float (&l)[2], float (&o)[DTILES][4]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NTILES; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = exp2f(m[h] - m_safe);
+    float sum = 0.f;
+#pragma unroll
+    for (int n = 0; n < NTILES; ++n) {
+      s[n][2 * h] = exp2f(s[n][2 * h] - m_safe);
+      s[n][2 * h + 1] = exp2f(s[n][2 * h + 1] - m_safe);
+      sum += s[n][2 * h] + s[n][2 * h + 1];
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    l[h] = l[h] * alpha + sum;
+    m[h] = m_new;
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n) {
+      o[n][2 * h] *= alpha;
+      o[n][2 * h + 1] *= alpha;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Many tokens per sequence. Block = (row tile of 64, kv head, sequence); warp w owns
+// rows 16w..16w+15 of the tile and walks all key blocks the tile can see.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
+                         const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                         const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
+                         int width, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, float scale_log2,
+                         int window) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);  // [2 stages][K, V][64][DP]
+  const int seq = blockIdx.z, kh = blockIdx.y;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // long tiles first
+  const int G = HQ / HKV;
+  const int q_len = seq_qlen[seq];
+  const int n_rows = q_len * G;
+  if (tile * 64 >= n_rows) return;
+  const int start = seq_start[seq], slot = seq_slot[seq], row0 = cu_q[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  // this thread's two rows
+  int tok[2], pos[2], lo[2];
+  const bf16* qp[2];
+  bf16* op[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int R = tile * 64 + warp * 16 + g + 8 * h;
+    const bool ok = R < n_rows;
+    tok[h] = ok ? R / G : -1;
+    const int head = kh * G + (ok ? R % G : 0);
+    pos[h] = ok ? start + tok[h] : -1;  // -1: sees nothing
+    lo[h] = (ok && window > 0) ? max(0, pos[h] - window + 1) : 0;
+    qp[h] = ok ? qkv + (size_t)(row0 + tok[h]) * q_stride + (size_t)head * D : nullptr;
+    op[h] = ok ? out + (size_t)(row0 + tok[h]) * HQ * D + (size_t)head * D : nullptr;
+  }
+  uint32_t qf[KSTEPS][4];
+  load_q(qf, qp[0], qp[1], lane);
+
+  // key blocks the tile can see
+  const int last_tok = min(q_len - 1, (tile * 64 + 63) / G);
+  const int first_tok = (tile * 64) / G;
+  const int j_hi = (start + last_tok) / KRK_PAGE;
+  const int j_lo = window > 0 ? max(0, start + first_tok - window + 1) / KRK_PAGE : 0;
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+  const size_t head_off = (size_t)kh * KRK_PAGE * D;
+
+  auto issue = [&](int j, int stage) {
+    const int page = table[(size_t)slot * width + j % width];
+    bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    load_page(ks, k_cache + (size_t)page * page_stride + head_off);
+    load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+    cp_async_commit();
+  };
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  issue(j_lo, 0);
+  for (int j = j_lo; j <= j_hi; ++j) {
+    const int stage = (j - j_lo) & 1;
+    if (j + 1 <= j_hi) {
+      issue(j + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    const bf16* vs = ks + TILE_ELEMS;
+    float s[8][4];
+    qk_tile<8>(s, qf, ks, 0, lane);
+    const int key_base = j * KRK_PAGE;
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = key_base + n * 8 + 2 * t4 + (c & 1);
+        const int h = c >> 1;
+        s[n][c] = (key <= pos[h] && key >= lo[h]) ? s[n][c] * scale_log2 : -INFINITY;
+      }
+    softmax_update<8>(s, m, l, o);
+    pv_tile<8>(o, s, vs, 0, lane);
+    __syncthreads();  // the stage is free for the load after next
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!op[h]) continue;
+    const float inv = 1.0f / l[h];
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n)
+      *reinterpret_cast<uint32_t*>(op[h] + n * 8 + 2 * t4) = pack_bf16x2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// One token per sequence. Block = (key split, kv head x row tile, sequence). The block
+// brings whole pages to shared memory; warp w works on keys 16w..16w+15 of each page
+// with running statistics of its own; the four warps merge at the end and the block
+// writes one partial (m, l, o[D]) per row, which the merge kernel combines.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+attention_decode_kernel(float* __restrict__ part, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
+                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                        const int* __restrict__ table, int width, const bf16* __restrict__ k_cache,
+                        const bf16* __restrict__ v_cache, float scale_log2, int window, int row_tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+  const int split = blockIdx.x, n_splits = gridDim.x;
+  const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
+  const int seq = blockIdx.z;
+  const int G = HQ / HKV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int pos = seq_start[seq], slot = seq_slot[seq];  // the new token sits at `pos`, its key is cached
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
+  const int n_blocks = j_last - j_first + 1;
+  const int per = (n_blocks + n_splits - 1) / n_splits;
+  const int j_lo = j_first + split * per, j_hi = min(j_last, j_lo + per - 1);
+
+  const bf16* qp[2];
+  int head[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = rt * 16 + g + 8 * h;
+    head[h] = r < G ? kh * G + r : -1;
+    qp[h] = r < G ? qkv + (size_t)seq * q_stride + (size_t)head[h] * D : nullptr;
+  }
+  uint32_t qf[KSTEPS][4];
+  load_q(qf, qp[0], qp[1], lane);
+
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+  const size_t head_off = (size_t)kh * KRK_PAGE * D;
+  auto issue = [&](int j, int stage) {
+    const int page = table[(size_t)slot * width + j % width];
+    bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    load_page(ks, k_cache + (size_t)page * page_stride + head_off);
+    load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+    cp_async_commit();
+  };
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  if (j_lo <= j_hi) issue(j_lo, 0);
+  for (int j = j_lo; j <= j_hi; ++j) {
+    const int stage = (j - j_lo) & 1;
+    if (j + 1 <= j_hi) {
+      issue(j + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    const bf16* vs = ks + TILE_ELEMS;
+    const int key0 = warp * 16;
+    float s[2][4];
+    qk_tile<2>(s, qf, ks, key0, lane);
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = j * KRK_PAGE + key0 + n * 8 + 2 * t4 + (c & 1);
+        s[n][c] = (key <= pos && key >= lo) ? s[n][c] * scale_log2 : -INFINITY;
+      }
+    softmax_update<2>(s, m, l, o);
+    pv_tile<2>(o, s, vs, key0, lane);
+    __syncthreads();
+  }
+
+  // merge the four warps: through shared memory, in warp order
+  float* red = reinterpret_cast<float*>(smem_raw);  // [4 warps][16 rows][D + 2]; the page buffers are free now
+  constexpr int RP = D + 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float* dst = red + ((size_t)warp * 16 + g + 8 * h) * RP;
+    if (t4 == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n) {
+      dst[n * 8 + 2 * t4] = o[n][2 * h];
+      dst[n * 8 + 2 * t4 + 1] = o[n][2 * h + 1];
+    }
+  }
+  __syncthreads();
+  for (int r = warp; r < 16; r += 4) {
+    const int row = rt * 16 + r;
+    if (row >= G) continue;
+    float mw[4], big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { mw[w] = red[((size_t)w * 16 + r) * RP + D]; big = fmaxf(big, mw[w]); }
+    const float safe = big == -INFINITY ? 0.f : big;
+    float wgt[4], lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
+    float* dst = part + (((size_t)seq * HQ + kh * G + row) * n_splits + split) * RP;
+    for (int d = lane; d < D; d += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+      dst[d] = acc;
+    }
+    if (lane == 0) { dst[D] = big; dst[D + 1] = lsum; }
+  }
+}
+
+// out[seq, head, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = 2^(m_s - max m): one warp per (seq, head).
+__global__ void attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part, int n_items, int n_splits) {
+  constexpr int RP = D + 2;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n_items) return;
+  const float* src = part + (size_t)item * n_splits * RP;
+  float big = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) big = fmaxf(big, src[(size_t)s * RP + D]);
+  float lsum = 0.f;
+  float acc[(D + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float w = exp2f(src[(size_t)s * RP + D] - big);
+    lsum += w * src[(size_t)s * RP + D + 1];
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) acc[i] += w * src[(size_t)s * RP + d];
+    }
+  }
+  const float inv = 1.0f / lsum;
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) out[(size_t)item * D + d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+constexpr size_t PAGE_SMEM = (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16);
+constexpr size_t RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
+constexpr size_t DECODE_SMEM = PAGE_SMEM > RED_SMEM ? PAGE_SMEM : RED_SMEM;
+
+}  // namespace
+
+// out [rows, HQ*D]; q rows are the first HQ*D elements of each qkv row (row stride q_stride elements).
+KRK_API int krk_attention_prefill(void* out, const void* qkv, int q_stride, int HQ, int HKV, const int* seq_slot,
+                                  const int* seq_start, const int* seq_qlen, const int* cu_q, const int* table,
+                                  int width, const void* k_cache, const void* v_cache, int n_seqs, int max_q_len,
+                                  float scale, int window, cudaStream_t stream) {
+  if (n_seqs == 0 || max_q_len == 0) return 0;
+  const int G = HQ / HKV;
+  const long long tiles = ((long long)max_q_len * G + 63) / 64;
+  if (tiles > 0x7fffffffLL || HKV > 65535 || n_seqs > 65535) return -3;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAGE_SMEM);
+    configured = true;
+  }
+  dim3 grid((unsigned)tiles, HKV, n_seqs);
+  attention_prefill_kernel<<<grid, THREADS, PAGE_SMEM, stream>>>(
+      (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
+      (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window);
+  KRK_CHECK_LAUNCH();
+  return 0;
+}
+
+// One token per sequence: row `seq` of qkv is sequence seq's token at position seq_start[seq].
+// part: float32 scratch of n_seqs * HQ * splits * (D + 2) elements.
+KRK_API int krk_attention_decode(void* out, const void* qkv, int q_stride, int HQ, int HKV, const int* seq_slot,
+                                 const int* seq_start, const int* table, int width, const void* k_cache,
+                                 const void* v_cache, int n_seqs, float scale, int window, int splits, void* part,
+                                 cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  const int G = HQ / HKV;
+  const int row_tiles = (G + 15) / 16;
+  if (HKV * row_tiles > 65535 || n_seqs > 65535 || splits < 1) return -3;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    configured = true;
+  }
+  dim3 grid(splits, HKV * row_tiles, n_seqs);
+  attention_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(
+      (float*)part, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, table, width, (const bf16*)k_cache,
+      (const bf16*)v_cache, scale * LOG2E, window, row_tiles);
+  KRK_CHECK_LAUNCH();
+  const int items = n_seqs * HQ;
+  attention_merge_kernel<<<(items + 3) / 4, 128, 0, stream>>>((bf16*)out, (const float*)part, items, splits);
+  KRK_CHECK_LAUNCH();
+  return 0;
+}
+
+#endif  // head size served by the tensor-core kernels

@@ -192,11 +192,27 @@ class Kernels:
         return (self.has_skinny and w.dtype == torch.bfloat16 and 0 < rows <= self.SKINNY_MAX_ROWS
                 and w.shape[1] % 32 == 0 and w.is_contiguous())
 
+    @staticmethod
+    def _fits_prologue(x) -> bool:
+        """Whether the normalised rows fit the fused kernel's shared memory."""
+        rows, k = x.shape
+        tiles = 1 if rows <= 8 else 2
+        return 8 * tiles * (k + 64) * 2 + 8 * 2 * tiles * 512 <= 200 * 1024
+
+    def _skinny_input(self, x):
+        """A Normed goes to the kernel as it is if its norm is still to be done and fits
+        the prologue; otherwise its rows are computed first."""
+        if isinstance(x, torch.Tensor):
+            return x
+        if x.done or not self._fits_prologue(x):
+            return x.tensor()
+        return x
+
     def linear(self, x, w, out_float32=False):
         """y = x W^T; W is [out, in]. x may be a Normed (see parts/norm.py)."""
         out_dtype = torch.float32 if out_float32 else w.dtype
-        if self._use_skinny(x, w) and (isinstance(x, torch.Tensor) or not x.done):
-            return self._skinny(x, w, out_dtype)
+        if self._use_skinny(x, w):
+            return self._skinny(self._skinny_input(x), w, out_dtype)
         x = self._resolve(x)
         if x.shape[0] == 0:
             return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
@@ -205,8 +221,8 @@ class Kernels:
         return torch.matmul(x, w.t())
 
     def gate_up_swiglu(self, h, w_gate_up, intermediate):
-        if self._use_skinny(h, w_gate_up) and (isinstance(h, torch.Tensor) or not h.done):
-            return self._skinny(h, w_gate_up, w_gate_up.dtype, swiglu_rows=intermediate)
+        if self._use_skinny(h, w_gate_up):
+            return self._skinny(self._skinny_input(h), w_gate_up, w_gate_up.dtype, swiglu_rows=intermediate)
         return self.swiglu(self.linear(h, w_gate_up), intermediate)
 
     # -- attention ------------------------------------------------------------------
@@ -230,7 +246,7 @@ class Kernels:
         win = int(window or 0)
         fast = qkv.dtype == torch.bfloat16 and head_dim % 16 == 0
         if fast and batch.is_decode and hasattr(lib, "krk_attention_decode"):
-            splits, parts = self._decode_partials(batch.n_seqs, heads, head_dim)
+            splits, parts = self._decode_partials(batch.n_seqs, heads, cache.kv_heads, head_dim)
             self._ok(lib.krk_attention_decode(
                 out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),
                 batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(),
@@ -250,11 +266,12 @@ class Kernels:
                 "attention")
         return out
 
-    def _decode_partials(self, n_seqs: int, heads: int, head_dim: int):
+    def _decode_partials(self, n_seqs: int, heads: int, kv_heads: int, head_dim: int):
         """Number of key splits for a decode step and the float32 scratch its partial
         results go through. The split count depends on the batch size only, never on
         lengths, so a captured step stays valid as sequences grow."""
-        splits = max(1, min(32, -(-296 // max(1, n_seqs * max(1, heads // 16 + (heads % 16 > 0))))))
+        row_tiles = -(-(heads // kv_heads) // 16)
+        splits = max(1, min(32, -(-296 // (n_seqs * kv_heads * row_tiles))))
         key = (n_seqs, heads, head_dim, splits)
         buf = self._partials.get(key)
         if buf is None:
