@@ -1,0 +1,258 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: the Qwen3-4B layer sizes with random weights (seeded normal(0, 0.02)),
+bfloat16, 64 cache slots of 4,096 positions; 1,024-token prompts of seeded uniform
+token ids are prefilled, then K decode steps are timed at batch 8 (``value``), and
+at batch 1 and 64 (``points``); a 2,048-token prompt is prefilled (``prefill``). A
+"step" is one decode step of the whole batch. One JSON line is printed.
+
+* ``value``: decoded tokens per second, timed on the device with CUDA events around
+  K steps that run without the host in between (captured step + selection kernel,
+  which feeds the next step).
+* ``e2e``: the same through ``Engine.generate``: every step copies its batch
+  description from pinned host memory and reads its tokens back to the host.
+* ``roofline``: bytes a decode step has to read (every weight once, the live
+  requests' keys and values at the mean context of the timed steps) over its time,
+  against the measured copy bandwidth.
+* ``prefill.frac``: the step's flops over its time over the measured bfloat16 peak.
+
+With --gpus above 1 it says that it runs on one GPU only and exits with 2. The
+reference cannot be installed offline (it has no setup.py or pyproject.toml), so
+--impl reference prints its ``unavailable`` line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+PROMPT = 1024
+PREFILL_TOKENS = 2048
+SLOTS, CONTEXT = 64, 4096
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    out = {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "source": "fallback"}
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            if raw.get("hbm_gbs"):
+                out["hbm_gbs"] = float(raw["hbm_gbs"])
+            if raw.get("bf16_tflops"):
+                out["bf16_tflops"] = float(raw["bf16_tflops"])
+            out["source"] = "measured"
+        except (ValueError, OSError):
+            pass
+    return out
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = ROOT / "gpurun_out"
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in text.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, layers: int) -> dict:
+    """Parameter bytes a decode step reads and flops per token of the linear layers."""
+    H, I, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    HQ, HKV, V = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.vocab_size
+    per_layer = (HQ + 2 * HKV) * D * H + H * HQ * D + 3 * I * H  # matrix elements
+    norms = layers * (2 * H + 2 * D) + H
+    head = V * H  # the output head; the embedding read is one row per token
+    weight_bytes = 2 * (layers * per_layer + head + norms)
+    kv_bytes_per_token = 2 * 2 * layers * HKV * D
+    return {"per_layer": per_layer, "weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token,
+            "head": head, "attn_dim": HQ * D}
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from kernel_rush_kawk_b200 import Engine, Qwen3Config, StepEntry
+
+    torch.cuda.set_device(0)
+    base = Qwen3Config.preset("qwen3_4b")
+    full_layers = base.num_hidden_layers
+    layers = args.layers or full_layers
+    cfg = Qwen3Config.from_dict({**base.to_dict(), "num_hidden_layers": layers})
+    pk = peaks()
+    t0 = time.time()
+    engine = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=SLOTS * CONTEXT, max_slots=SLOTS,
+                                max_context=CONTEXT)
+    ops, cache, stepper = engine.ops, engine.cache, engine.stepper
+    numbers = model_numbers(cfg, layers)
+    gen = torch.Generator().manual_seed(1234)
+
+    def prompts(n, length):
+        return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
+
+    def decode_point(batch: int, steps: int, warmup: int):
+        """Prefill `batch` prompts, then time `steps` device-fed decode steps. Returns
+        (tokens per second, ms per step, launches per step, mean context)."""
+        slots = [cache.alloc() for _ in range(batch)]
+        try:
+            for i in range(0, batch, 8):  # prompts go in by eights to bound activation memory
+                chunk = slots[i:i + 8]
+                logits = engine.step([StepEntry(s, p, [PROMPT - 1]) for s, p in zip(chunk, prompts(len(chunk), PROMPT))])
+                first = logits.argmax(dim=-1).tolist() if i == 0 else first + logits.argmax(dim=-1).tolist()
+            toks = stepper.decode_on_device(slots, first, warmup)
+            first = toks[-1].tolist()
+            torch.cuda.synchronize()
+            before = ops.launches
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            stepper.decode_on_device(slots, first, steps, first_step=warmup)
+            end.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(end) / steps
+            graph_launches = stepper.graph_launches.get(batch, 0)
+            launches = graph_launches + (ops.launches - before) / steps
+            mean_ctx = PROMPT + warmup + (steps + 1) / 2
+            return batch * 1000.0 / ms, ms, launches, mean_ctx
+        finally:
+            for s in slots:
+                cache.free(s)
+
+    # -- headline: batch 8 -------------------------------------------------------
+    sampler = ClockSampler()
+    sampler.start()
+    value, ms_step, launches, mean_ctx = decode_point(8, args.steps, args.warmup)
+    clocks = sampler.stop()
+    step_bytes = numbers["weight_bytes"] + 8 * mean_ctx * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+
+    # -- end to end through the entry point, batch 8 -----------------------------------
+    e2e_prompts = prompts(8, PROMPT)
+    it = engine.generate(e2e_prompts, args.warmup + args.steps)
+    for _ in range(args.warmup):
+        next(it)
+    torch.cuda.synchronize()
+    t_start = time.perf_counter()
+    n = 0
+    for _ in it:
+        n += 1
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t_start) * 1000.0 / max(n, 1)
+    e2e = {"value": round(8 * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": stepper.h2d_bytes, "d2h_bytes_per_step": 8 * 4}
+
+    # -- the other batch sizes -------------------------------------------------------
+    points = {}
+    for b in (1, 64):
+        v, ms_b, _, ctx_b = decode_point(b, args.steps, args.warmup)
+        bytes_b = numbers["weight_bytes"] + b * ctx_b * numbers["kv_bytes_per_token"]
+        points[f"decode_b{b}"] = round(v, 1)
+        points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+
+    # -- prefill of 2,048 tokens ---------------------------------------------------------
+    prompt = prompts(1, PREFILL_TOKENS)[0]
+    times = []
+    for i in range(args.warmup + 5):
+        slot = cache.alloc()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        cache.free(slot)
+        if i >= args.warmup:
+            times.append(start.elapsed_time(end))
+    pre_ms = statistics.median(times)
+    T = PREFILL_TOKENS
+    flops = 2 * T * layers * numbers["per_layer"] + 2 * numbers["head"] + layers * 4 * numbers["attn_dim"] * T * (T + 1) / 2
+    prefill = {"value": round(T * 1000.0 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    return {
+        "metric": "decode tokens/s at batch 8 (Qwen3-4B shape, 1,024-token prompts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights normal(0, 0.02), seeded uniform token ids",
+        "config": {"model": "qwen3-4b-shape", "layers": layers, "layers_of_model": full_layers,
+                   "hidden": cfg.hidden_size, "intermediate": cfg.intermediate_size, "q_heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "vocab": cfg.vocab_size,
+                   "tied_head": cfg.tie_word_embeddings, "global_batch": 8, "prompt_len": PROMPT,
+                   "seq_len": CONTEXT, "slots": SLOTS, "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2: a step reads %.1f GB" % (step_bytes / 1e9),
+                   "peaks": pk["source"], "hbm_peak_gbs": pk["hbm_gbs"], "bf16_peak_tflops": pk["bf16_tflops"]},
+        "e2e": e2e, "gpu_launches": int(round(launches * args.steps)), "launches_per_step": round(launches, 1),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "points": points, "clocks": clocks, "impl": "ours", "load_s": round(time.time() - t0, 1),
+    }
+
+
+def main() -> int:
+    p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=128)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
+    args = p.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is not installable offline: pip finds neither "
+                          "setup.py nor pyproject.toml in it (it is a source-only Triton/H100 submission)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py runs on one GPU only (this library has no multi-GPU path); got --gpus {args.gpus}")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "krk_qk_norm_rope_write": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int,
                                c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
-    "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P],
+    "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -280,12 +280,17 @@ class Kernels:
         return splits, buf
 
     # -- token selection ------------------------------------------------------------
-    def select_tokens(self, logits, temperature, seed, requests, step):
+    def select_tokens(self, logits, temperature, seed, requests, step, feed=None, out=None):
+        """One token per row. ``feed``: the batch description of a single-token step; the
+        kernel then also writes the chosen tokens into it and moves its positions on by
+        one, so that the next step can run without the host."""
         n, vocab = logits.shape
-        tokens = torch.empty(n, dtype=torch.int32, device=logits.device)
+        tokens = out if out is not None else torch.empty(n, dtype=torch.int32, device=logits.device)
         logits = logits.contiguous()
+        f = (None, None, None) if feed is None else (feed.tokens.data_ptr(), feed.row_pos.data_ptr(),
+                                                     feed.seq_start.data_ptr())
         self._ok(self.core.krk_select_tokens(tokens.data_ptr(), logits.data_ptr(), n, vocab, temperature,
-                                             seed & 0xFFFFFFFF, requests.data_ptr(), step & 0xFFFFFFFF,
+                                             seed & 0xFFFFFFFF, requests.data_ptr(), step & 0xFFFFFFFF, *f,
                                              self._stream()), "token selection")
         return tokens
 

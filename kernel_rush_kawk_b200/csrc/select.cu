@@ -22,7 +22,8 @@ __host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
 
 __global__ void select_tokens_kernel(int* __restrict__ tokens, const float* __restrict__ logits, int vocab,
                                      float temperature, uint32_t seed, const int* __restrict__ requests,
-                                     uint32_t step) {
+                                     uint32_t step, int* __restrict__ feed_tokens, int* __restrict__ feed_pos,
+                                     int* __restrict__ feed_start) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
   const int row = blockIdx.x;
@@ -60,16 +61,28 @@ __global__ void select_tokens_kernel(int* __restrict__ tokens, const float* __re
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) tokens[row] = bi == 0x7fffffff ? 0 : bi;
+    if (lane == 0) {
+      const int tok = bi == 0x7fffffff ? 0 : bi;
+      tokens[row] = tok;
+      if (feed_tokens) {  // feed the next single-token step on the device: its token, its position
+        feed_tokens[row] = tok;
+        feed_pos[row] += 1;
+        feed_start[row] += 1;
+      }
+    }
   }
 }
 
 }  // namespace
 
+// feed_*: null, or the token / row position / sequence start arrays of a single-token step's batch
+// description, which then describe the next step: token = the selected one, positions + 1.
 KRK_API int krk_select_tokens(int* tokens, const float* logits, int rows, int vocab, float temperature, unsigned seed,
-                              const int* requests, unsigned step, cudaStream_t stream) {
+                              const int* requests, unsigned step, int* feed_tokens, int* feed_pos, int* feed_start,
+                              cudaStream_t stream) {
   if (rows == 0) return 0;
-  select_tokens_kernel<<<rows, 1024, 0, stream>>>(tokens, logits, vocab, temperature, seed, requests, step);
+  select_tokens_kernel<<<rows, 1024, 0, stream>>>(tokens, logits, vocab, temperature, seed, requests, step,
+                                                  feed_tokens, feed_pos, feed_start);
   KRK_CHECK_LAUNCH();
   return 0;
 }

@@ -130,6 +130,7 @@ class Stepper:
         self.vocab = model.plan.vocab_size
         self._graphs: dict[int, _DecodeGraph] = {}
         self._metas: dict[tuple, list] = {}
+        self.graph_launches: dict[int, int] = {}  # kernels of this package inside each captured step
         self.h2d_bytes = 0  # bytes of the last step's host-to-device copies
         self.passes = 0
 
@@ -255,6 +256,41 @@ class Stepper:
         idx = torch.as_tensor(want_rows, dtype=torch.int64, device=self.device)
         return g.logits.index_select(0, idx)
 
+    def decode_on_device(self, slots, tokens, n_steps: int, temperature: float = 0.0, seed: int = 0,
+                         requests=None, first_step: int = 0) -> torch.Tensor:
+        """``n_steps`` single-token steps without a host round trip: the selection kernel
+        writes each step's tokens into the next step's batch description. Returns the
+        chosen tokens, int32 [n_steps, sequences], on the device. Pages for all steps
+        are reserved before the first one."""
+        n = len(slots)
+        cache = self.cache
+        starts = [cache.length[s] for s in slots]
+        for s in slots:
+            cache.reserve(s, cache.length[s] + n_steps)
+        cache.sync()
+        token_lists = [[int(t)] for t in tokens]
+        if self.use_graphs:
+            g = self._graphs.get(n) or self._capture(n, slots, starts, token_lists)
+            meta = g.meta
+        else:
+            g, meta = None, self._meta(n, n, n)
+        meta.fill(slots, starts, token_lists, list(range(n)))
+        self.h2d_bytes = meta.bytes
+        req = torch.tensor(list(requests) if requests is not None else list(range(n)), dtype=torch.int32).to(self.device)
+        out = torch.empty((n_steps, n), dtype=torch.int32, device=self.device)
+        ctx = StepContext(self.ops, meta, cache)
+        for t in range(n_steps):
+            if g is not None:
+                g.graph.replay()
+                logits = g.logits
+            else:
+                logits = self.model.forward(ctx, meta.want)
+            self.ops.select_tokens(logits, temperature, seed, req, first_step + t, feed=meta, out=out[t])
+        for s in slots:
+            cache.advance(s, n_steps)
+        self.passes += n_steps
+        return out
+
     def _capture(self, n: int, slots, starts, token_lists) -> _DecodeGraph:
         meta = BatchMeta(n, n, n, self.device)
         meta.fill(slots, starts, token_lists, list(range(n)))
@@ -269,7 +305,9 @@ class Stepper:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        before = getattr(self.ops, "launches", 0)
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx, meta.want)
+        self.graph_launches[n] = getattr(self.ops, "launches", 0) - before
         g = self._graphs[n] = _DecodeGraph(graph, meta, logits)
         return g
