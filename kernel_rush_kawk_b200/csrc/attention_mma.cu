@@ -432,3 +432,70 @@ KRK_API int krk_attention_decode(void* out, const void* qkv, int q_stride, int H
 }
 
 #endif  // head size served by the tensor-core kernels
+
+// ---------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate: the partial results
+// live in a fixed array of this library (see attention_noalloc.h for who needs this,
+// the limits, and the rules on first call and on overlapping calls).
+// ---------------------------------------------------------------------------------
+#if KRK_HEAD_DIM % 16 == 0 && KRK_HEAD_DIM <= 256
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float krk_noalloc_scratch[KRK_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// Device address of the array per device. In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use.
+float* noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) const char* krk_attention_decode_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -3: return "the grid would be too large (too many kv heads or sequences), or splits < 1";
+    case KRK_NOALLOC_TOO_LARGE:
+      return "n_seqs * HQ * splits * (head_dim + 2) floats exceed the library's fixed 4 MiB scratch; "
+             "use fewer splits or sequences per call, or krk_attention_decode with a scratch buffer of your own";
+    case KRK_NOALLOC_SETUP_FAILED: return "the device address of the scratch array could not be obtained";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
+  }
+}
+
+extern "C" __attribute__((visibility("default"))) int krk_attention_decode_noalloc(
+    void* out, const void* qkv, int q_stride, int HQ, int HKV, const int* seq_slot, const int* seq_start,
+    const int* table, int width, const void* k_cache, const void* v_cache, int n_seqs, float scale, int window,
+    int splits, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  const int G = HQ / HKV;
+  const int row_tiles = (G + 15) / 16;
+  if (HKV * row_tiles > 65535 || n_seqs > 65535 || splits < 1) return -3;
+  const unsigned long long need = (unsigned long long)n_seqs * HQ * splits * (D + 2) * sizeof(float);
+  if (need > KRK_NOALLOC_SCRATCH_BYTES) return KRK_NOALLOC_TOO_LARGE;
+
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return (int)err;
+  if (device < 0 || device >= NOALLOC_MAX_DEVICES) return KRK_NOALLOC_SETUP_FAILED;
+  if (noalloc_scratch_ptr[device] == nullptr) {  // once per device, with that device current
+    float* p = nullptr;
+    err = cudaGetSymbolAddress((void**)&p, krk_noalloc_scratch);
+    if (err != cudaSuccess) return (int)err;
+    if (p == nullptr) return KRK_NOALLOC_SETUP_FAILED;
+    err = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    if (err != cudaSuccess) return (int)err;
+    noalloc_scratch_ptr[device] = p;
+  }
+  float* part = noalloc_scratch_ptr[device];
+
+  dim3 grid(splits, HKV * row_tiles, n_seqs);
+  attention_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(
+      part, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, table, width, (const bf16*)k_cache,
+      (const bf16*)v_cache, scale * LOG2E, window, row_tiles);
+  KRK_CHECK_LAUNCH();
+  const int items = n_seqs * HQ;
+  attention_merge_kernel<<<(items + 3) / 4, 128, 0, stream>>>((bf16*)out, part, items, splits);
+  KRK_CHECK_LAUNCH();
+  return 0;
+}
+#endif
