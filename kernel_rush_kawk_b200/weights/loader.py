@@ -95,9 +95,10 @@ def read_checkpoint(folder, expected: dict, device, compute: torch.dtype, duplic
                     spare[name] = f.get_tensor(name)
                 else:
                     unexpected.append(name)
-    for name, same_as in spare.items():
-        if same_as in found and spare[name].shape == found[same_as].shape and torch.equal(
-                spare[name].to(found[same_as].dtype), found[same_as].cpu()):
+    for name, tensor in spare.items():
+        same_as = duplicates[name]
+        if same_as in found and tensor.shape == found[same_as].shape and torch.equal(
+                tensor.to(found[same_as].dtype), found[same_as].cpu()):
             continue
         other.append(f"{name} is present although the model ties it to {same_as}, and differs from it")
     missing = [n for n in expected if n not in found and n not in wrong_shape]
