@@ -18,6 +18,7 @@ calls.
 from __future__ import annotations
 
 import logging
+import os
 import time
 from pathlib import Path
 
@@ -93,7 +94,8 @@ class Engine:
         self.model = Model(self.plan, Runtime(self.device, self.dtype, self.ops), tensors, self.max_context)
         self.max_slots = int(max_slots)
         self.max_tokens = max_tokens
-        self.use_cuda_graphs = use_cuda_graphs
+        # the reference's own switch, same name and meaning (engine/engine.py:487)
+        self.use_cuda_graphs = bool(use_cuda_graphs) and os.environ.get("ENGINE_NO_GRAPHS") is None
         self.max_step_rows = max_step_rows
         self.cache = self.stepper = self.loop = None
         self.sampler = Sampler(self.ops, self.device)

@@ -32,8 +32,10 @@ class RotaryTable(PositionEncoding):
         self.cos, self.sin = self.build(self.positions, runtime.device, runtime.dtype)
 
     def build(self, positions: int, device, dtype):
-        exponent = torch.arange(0, self.dim, 2, dtype=torch.int64, device=device).to(torch.float32) / self.dim
-        inv_freq = 1.0 / (self.theta ** exponent)
+        # the few inverse frequencies are computed on the host, so that the table does not
+        # depend on a device's pow(); products, cos and sin run on the device in float32
+        exponent = torch.arange(0, self.dim, 2, dtype=torch.int64).to(torch.float32) / self.dim
+        inv_freq = (1.0 / (self.theta ** exponent)).to(device)
         pos = torch.arange(positions, dtype=torch.float32, device=device)
         angle = pos[:, None] * inv_freq[None, :]
         return angle.cos().to(dtype).contiguous(), angle.sin().to(dtype).contiguous()

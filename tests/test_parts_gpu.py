@@ -1,0 +1,320 @@
+"""Each part alone against the plain implementation, and the generality of the
+assembly: a toy mixer with state of its own, a layer that runs twice, a run that
+reads another run's cache -- registered, built and stepped from this file without
+a change to the package."""
+
+import math
+from dataclasses import dataclass
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = (torch.float32, torch.bfloat16)
+NAME = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+
+
+def runtime(dtype):
+    from kernel_rush_kawk_b200.csrc import load_kernels
+    from kernel_rush_kawk_b200.engine.model import Runtime
+
+    return Runtime(torch.device("cuda:0"), dtype, load_kernels(()))
+
+
+def rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g) * scale
+
+
+def context(rt, slots, starts, q_lens, cache):
+    from kernel_rush_kawk_b200.engine.step import BatchMeta, StepContext
+
+    rows = sum(q_lens)
+    meta = BatchMeta(rows, len(slots), 0, rt.device)
+    meta.fill(slots, starts, [[0] * n for n in q_lens], [])
+    return StepContext(rt.ops, meta, cache)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_part_folds_the_pending_branch(dtype):
+    from kernel_rush_kawk_b200.parts import RMSNorm, Stream
+
+    rt = runtime(dtype)
+    rounding = None if dtype == torch.float32 else torch.bfloat16
+    part = RMSNorm({"size": 100, "eps": 1e-5})
+    gain = (1 + 0.1 * rand((100,), 1)).to(dtype)
+    part.bind({"weight": gain.cuda()}, rt)
+    x, b = rand((6, 100), 2, 3.0).to(dtype), rand((6, 100), 3).to(dtype)
+    ctx = SimpleNamespace(ops=rt.ops)
+    stream = Stream(x.cuda(), b.cuda())
+    h = part.forward(ctx, stream).tensor()
+    s = plain.residual_add(x.float(), b.float(), rounding)
+    assert stream.branch is None and torch.equal(stream.x.float().cpu(), s)
+    assert_close(h, plain.rms_norm(s, gain.float(), 1e-5, rounding), NAME[dtype], "norm part", kernel=True)
+    alone = part.forward(ctx, Stream(x.cuda())).tensor()
+    assert_close(alone, plain.rms_norm(x.float(), gain.float(), 1e-5, rounding), NAME[dtype], "norm part", kernel=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rotary_table_part(dtype):
+    from kernel_rush_kawk_b200.parts import RotaryTable
+
+    part = RotaryTable({"theta": 5e5, "dim": 48, "positions": 300})
+    part.bind({}, runtime(dtype))
+    cos, sin = part.rotary_tables()
+    pc, ps = plain.rope_tables(48, 5e5, 300, torch.float32, None if dtype == torch.float32 else torch.bfloat16)
+    assert cos.shape == (300, 24) and cos.dtype == dtype
+    assert (cos.float().cpu() - pc).abs().max() < (1e-5 if dtype == torch.float32 else 8e-3)
+    assert (sin.float().cpu() - ps).abs().max() < (1e-5 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 20])
+def test_attention_part_alone(dtype, window):
+    """hidden 72, 6 heads in 3 groups, head size 16 (6*16 != 72); a whole sequence in one
+    step, then the same sequence in two steps."""
+    from kernel_rush_kawk_b200.cache import SequenceCache
+    from kernel_rush_kawk_b200.parts import GQAttention, RotaryTable
+
+    rt = runtime(dtype)
+    rounding = None if dtype == torch.float32 else torch.bfloat16
+    H, HQ, HKV, D, T = 72, 6, 3, 16, 90
+    part = GQAttention({"hidden": H, "heads": HQ, "kv_heads": HKV, "head_dim": D, "eps": 1e-6, "window": window})
+    rope = RotaryTable({"theta": 1e4, "dim": D, "positions": 256})
+    rope.bind({}, rt)
+    part.set_position(rope)
+    w = {"q_proj": rand((HQ * D, H), 1, 0.1), "k_proj": rand((HKV * D, H), 2, 0.1), "v_proj": rand((HKV * D, H), 3, 0.1),
+         "o_proj": rand((H, HQ * D), 4, 0.1), "q_norm": 1.5 + 0.1 * rand((D,), 5), "k_norm": 1.5 + 0.1 * rand((D,), 6)}
+    w = {k: v.to(dtype) for k, v in w.items()}
+    assert {k: tuple(s.shape) for k, s in part.tensor_specs().items()} == {k: tuple(v.shape) for k, v in w.items()}
+    part.bind({k: v.cuda() for k, v in w.items()}, rt)
+    h = rand((T, H), 7).to(dtype)
+    cfg = plain.PlainConfig(H, 0, 1, HQ, HKV, D, 0, 1e-6, 1e4, False)
+    names = {f"L.self_attn.{k}.weight": v.float() for k, v in w.items()}
+    pc, ps = plain.rope_tables(D, 1e4, T, torch.float32, rounding)
+    want = plain.attention_block(h.float(), names, "L.", cfg, pc, ps, window, rounding)
+    for pieces in ([T], [50, 40]):
+        cache = SequenceCache([part.cache_need()], 256, 2, 256, rt.device, dtype, step_tokens=64)
+        slot = cache.alloc()
+        got, start = [], 0
+        for n in pieces:
+            cache.reserve(slot, start + n)
+            cache.sync()
+            ctx = context(rt, [slot], [start], [n], cache)
+            got.append(part.forward(ctx, h[start:start + n].cuda(), cache.view(0)))
+            cache.advance(slot, n)
+            start += n
+        assert_close(torch.cat(got), want, NAME[dtype], f"attention part, pieces {pieces}", kernel=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_part_and_block_alone(dtype):
+    from kernel_rush_kawk_b200.cache import SequenceCache
+    from kernel_rush_kawk_b200.parts import GQAttention, PreNormBlock, RMSNorm, RotaryTable, Stream, SwiGLU
+
+    rt = runtime(dtype)
+    rounding = None if dtype == torch.float32 else torch.bfloat16
+    H, I, HQ, HKV, D, T = 80, 208, 5, 1, 16, 40
+    ffn = SwiGLU({"hidden": H, "intermediate": I})
+    wf = {"gate_proj": rand((I, H), 1, 0.1).to(dtype), "up_proj": rand((I, H), 2, 0.1).to(dtype),
+          "down_proj": rand((H, I), 3, 0.1).to(dtype)}
+    ffn.bind({k: v.cuda() for k, v in wf.items()}, rt)
+    h = rand((T, H), 4).to(dtype)
+    ctx = SimpleNamespace(ops=rt.ops)
+    want = plain.swiglu_mlp(h.float(), wf["gate_proj"].float(), wf["up_proj"].float(), wf["down_proj"].float(), rounding)
+    assert_close(ffn.forward(ctx, h.cuda()), want, NAME[dtype], "swiglu part", kernel=True)
+
+    attn = GQAttention({"hidden": H, "heads": HQ, "kv_heads": HKV, "head_dim": D, "eps": 1e-5})
+    rope = RotaryTable({"theta": 1e6, "dim": D, "positions": 128})
+    rope.bind({}, rt)
+    attn.set_position(rope)
+    wa = {"q_proj": rand((HQ * D, H), 5, 0.1), "k_proj": rand((HKV * D, H), 6, 0.1), "v_proj": rand((HKV * D, H), 7, 0.1),
+          "o_proj": rand((H, HQ * D), 8, 0.1), "q_norm": 1 + 0.1 * rand((D,), 9), "k_norm": 1 + 0.1 * rand((D,), 10)}
+    wa = {k: v.to(dtype) for k, v in wa.items()}
+    attn.bind({k: v.cuda() for k, v in wa.items()}, rt)
+    n1, n2 = RMSNorm({"size": H, "eps": 1e-5}), RMSNorm({"size": H, "eps": 1e-5})
+    g1, g2 = (1 + 0.1 * rand((H,), 11)).to(dtype), (1 + 0.1 * rand((H,), 12)).to(dtype)
+    n1.bind({"weight": g1.cuda()}, rt)
+    n2.bind({"weight": g2.cuda()}, rt)
+    block = PreNormBlock(n1, attn, n2, ffn)
+    cache = SequenceCache([attn.cache_need()], 128, 1, 128, rt.device, dtype)
+    slot = cache.alloc()
+    cache.reserve(slot, T)
+    cache.sync()
+    x = rand((T, H), 13).to(dtype)
+    stream = block.forward(context(rt, [slot], [0], [T], cache), Stream(x.cuda()), cache.view(0))
+    got = plain.residual_add(stream.x.float().cpu(), stream.branch.float().cpu(), rounding)
+    cfg = plain.PlainConfig(H, I, 1, HQ, HKV, D, 0, 1e-5, 1e6, False)
+    names = {f"model.layers.0.self_attn.{k}.weight": v.float() for k, v in wa.items()}
+    names.update({f"model.layers.0.mlp.{k}.weight": v.float() for k, v in wf.items()})
+    names["model.layers.0.input_layernorm.weight"] = g1.float()
+    names["model.layers.0.post_attention_layernorm.weight"] = g2.float()
+    pc, ps = plain.rope_tables(D, 1e6, T, torch.float32, rounding)
+    want = plain.decoder_layer(x.float(), names, 0, cfg, pc, ps, None, rounding)
+    assert_close(got, want, NAME[dtype], "block alone", kernel=True)
+
+
+# ---------------------------------------------------------------------------------
+# A toy architecture defined here: layer 0 attention, layer 1 a mixer with state of its
+# own, layer 2 attention that reads run 1's... and a schedule that names layer 0 twice.
+# ---------------------------------------------------------------------------------
+def register_toy():
+    from kernel_rush_kawk_b200.config import ModelConfig, register_architecture
+    from kernel_rush_kawk_b200.parts import (LayerSpec, Mixer, ModelPlan, PartSpec, ScheduleEntry, StateNeed, TensorSpec,
+                                             register_mixer)
+
+    class DecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + h_t (state [hidden] per sequence, float32); out_t = s_t W^T."""
+
+        graph_safe = False  # reads the step's host-side lengths
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.hidden, self.decay = int(params["hidden"]), float(params["decay"])
+
+        def tensor_specs(self):
+            return {"mix": TensorSpec((self.hidden, self.hidden))}
+
+        def cache_need(self):
+            return StateNeed((self.hidden,), "float32")
+
+        def bind(self, tensors, runtime):
+            self.w = tensors["mix"]
+
+        def forward(self, ctx, h, cache):
+            rows = h.tensor().float()
+            out = torch.empty_like(rows)
+            r = 0
+            for slot, n in zip(ctx.batch.slots, ctx.batch.q_lens):
+                s = cache.state[slot]
+                for t in range(n):
+                    s = self.decay * s + rows[r + t]
+                    out[r + t] = s
+                cache.state[slot] = s
+                r += n
+            return (out.to(self.w.dtype).float() @ self.w.float().t()).to(self.w.dtype)
+
+    register_mixer("test_decay", DecayMixer)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        hidden: int = 48
+        vocab: int = 97
+        architecture = "ToyDecoderForTests"
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw.get("hidden", 48), raw.get("vocab", 97))
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "hidden": self.hidden, "vocab": self.vocab}
+
+    def plan(cfg):
+        H = cfg.hidden
+        norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": name})
+        ffn = lambda i: PartSpec("swiglu", {"hidden": H, "intermediate": 64},
+                                 {k: f"l{i}.ffn.{k}" for k in ("gate_proj", "up_proj", "down_proj")})
+        attn = lambda i, own: PartSpec(
+            "gqa_attention", {"hidden": H, "heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-5, "own_cache": own},
+            {k: f"l{i}.attn.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
+        layers = [
+            LayerSpec("prenorm", norm("l0.n1"), attn(0, True), norm("l0.n2"), ffn(0)),
+            LayerSpec("prenorm", norm("l1.n1"), PartSpec("test_decay", {"hidden": H, "decay": 0.5}, {"mix": "l1.mix"}),
+                      norm("l1.n2"), ffn(1)),
+            LayerSpec("prenorm", norm("l2.n1"), attn(2, False), norm("l2.n2"), ffn(2)),
+        ]
+        # layer 0 runs twice (two caches), the state mixer in between, then a layer with
+        # queries only that reads the keys and values of the second run of layer 0
+        schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, cache_from=2)]
+        return ModelPlan("ToyDecoderForTests", H, cfg.vocab,
+                         PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": H}, {"table": "embed"}),
+                         PartSpec("rope", {"theta": 1e4, "dim": 16}), tuple(layers), tuple(schedule), norm("final"),
+                         PartSpec("output_head", {"vocab": cfg.vocab, "hidden": H}, {"weight": "embed"}), 512)
+
+    register_architecture("ToyDecoderForTests", ToyConfig, plan)
+    return ToyConfig()
+
+
+def toy_plain(w, ids, rounding):
+    """The toy model, whole sequence, from the plain implementation's functions."""
+    rt = (lambda t: t) if rounding is None else (lambda t: t.to(rounding).float())
+    T = len(ids)
+    cos, sin = plain.rope_tables(16, 1e4, T, torch.float32, rounding)
+    cfg = SimpleNamespace(heads=4, kv_heads=2, head_dim=16, eps=1e-5)
+    x = w["embed"][torch.tensor(ids)]
+
+    def attn(h, i, kv=None):
+        q = plain.linear(h, w[f"l{i}.attn.q_proj"], rounding).view(T, 4, 16)
+        q = plain.head_norm_rope(q, w[f"l{i}.attn.q_norm"], cos, sin, 1e-5, rounding)
+        if kv is None:
+            k = plain.linear(h, w[f"l{i}.attn.k_proj"], rounding).view(T, 2, 16)
+            v = plain.linear(h, w[f"l{i}.attn.v_proj"], rounding).view(T, 2, 16)
+            kv = (plain.head_norm_rope(k, w[f"l{i}.attn.k_norm"], cos, sin, 1e-5, rounding), v)
+        a = plain.causal_gqa_attention(q, kv[0], kv[1], None, rounding)
+        return plain.linear(a, w[f"l{i}.attn.o_proj"], rounding), kv
+
+    def decay(h):
+        s, out = torch.zeros(h.shape[1]), []
+        for t in range(T):
+            s = 0.5 * s + h[t]
+            out.append(s)
+        return rt(rt(torch.stack(out)) @ w["l1.mix"].t())
+
+    def ffn(x, i):
+        h = plain.rms_norm(x, w[f"l{i}.n2"], 1e-5, rounding)
+        d = plain.swiglu_mlp(h, w[f"l{i}.ffn.gate_proj"], w[f"l{i}.ffn.up_proj"], w[f"l{i}.ffn.down_proj"], rounding)
+        return plain.residual_add(x, d, rounding)
+
+    kv2 = None
+    for run, layer in enumerate((0, 1, 0, 2)):
+        h = plain.rms_norm(x, w[f"l{layer}.n1"], 1e-5, rounding)
+        if layer == 1:
+            branch = decay(h)
+        elif layer == 2:
+            branch, _ = attn(h, 2, kv2)
+        else:
+            branch, kv = attn(h, 0)
+            if run == 2:
+                kv2 = kv
+        x = ffn(plain.residual_add(x, branch, rounding), layer)
+    return plain.rms_norm(x, w["final"], 1e-5, rounding) @ w["embed"].t()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_architecture_with_a_state_mixer_a_repeated_layer_and_a_shared_cache(dtype, tmp_path):
+    from kernel_rush_kawk_b200 import Engine, StepEntry, write_model_folder
+    from safetensors.torch import load_file
+
+    cfg = register_toy()
+    folder = write_model_folder(tmp_path / "toy", cfg, 5, std=0.08, gain_std=0.1)
+    engine = Engine(folder, dtype=NAME[dtype], max_tokens=1024, max_slots=4)
+    assert not engine.model.graph_safe and not engine.stepper.use_graphs
+    assert "l2.attn.k_proj" not in load_file(str(folder / "model.safetensors"))  # queries only
+    w = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (70, 9)]
+    refs = [toy_plain(w, s, None if dtype == torch.float32 else torch.bfloat16) for s in seqs]
+    # whole, then prompt + single tokens in an unequal batch
+    for cuts in ([70, 9], [40, 3]):
+        slots = [engine.cache.alloc() for _ in seqs]
+        got = [[] for _ in seqs]
+        out = engine.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cuts)])
+        got[0].append(out[:cuts[0]]); got[1].append(out[cuts[0]:])
+        fed = list(cuts)
+        while any(f < len(s) for f, s in zip(fed, seqs)):
+            live = [i for i in range(2) if fed[i] < len(seqs[i])]
+            out = engine.step([StepEntry(slots[i], [seqs[i][fed[i]]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1]); fed[i] += 1
+        for i in range(2):
+            assert_close(torch.cat(got[i]), refs[i], NAME[dtype], f"toy model, cuts {cuts}, request {i}")
+        for s in slots:
+            engine.cache.free(s)
+    engine.cache.check()
+    toks = list(engine.generate([seqs[1]], 3))
+    assert len(toks) == 3
