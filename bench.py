@@ -164,6 +164,23 @@ def run_ours(args) -> dict:
             for s in slots:
                 cache.free(s)
 
+    if args.only:  # one piece only, for profiling runs: prints a short line of its own
+        if args.only == "prefill":
+            prompt = prompts(1, PREFILL_TOKENS)[0]
+            for _ in range(args.warmup + args.steps):
+                slot = cache.alloc()
+                torch.cuda.synchronize()
+                t = time.perf_counter()
+                engine.step([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+                torch.cuda.synchronize()
+                ms = (time.perf_counter() - t) * 1e3
+                cache.free(slot)
+            return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms_last": round(ms, 3), "layers": layers}
+        b = int(args.only.split("_b")[1])
+        v, ms_b, launches, _ = decode_point(b, args.steps, args.warmup)
+        return {"only": args.only, "value": round(v, 1), "ms_per_step": round(ms_b, 4), "launches_per_step": launches,
+                "layers": layers}
+
     # -- headline: batch 8 -------------------------------------------------------
     sampler = ClockSampler()
     sampler.start()
@@ -240,6 +257,8 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=128)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b64"],
+                   help="run one piece only (for profiling)")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()
     if args.impl == "reference":

@@ -244,6 +244,8 @@ attention_decode_kernel(float* __restrict__ part, const bf16* __restrict__ qkv, 
                         const bf16* __restrict__ v_cache, float scale_log2, int window, int row_tiles) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int split = blockIdx.x, n_splits = gridDim.x;
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
   const int seq = blockIdx.z;
@@ -350,19 +352,25 @@ attention_decode_kernel(float* __restrict__ part, const bf16* __restrict__ qkv, 
 // out[seq, head, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = 2^(m_s - max m): one warp per (seq, head).
 __global__ void attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part, int n_items, int n_splits) {
   constexpr int RP = D + 2;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= n_items) return;
   const float* src = part + (size_t)item * n_splits * RP;
+  // statistics: lane s reads split s, s + 32, ...; all loads are independent
   float big = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) big = fmaxf(big, src[(size_t)s * RP + D]);
+  for (int s = lane; s < n_splits; s += 32) big = fmaxf(big, src[(size_t)s * RP + D]);
+  big = warp_max(big);
   float lsum = 0.f;
+  for (int s = lane; s < n_splits; s += 32) lsum += exp2f(src[(size_t)s * RP + D] - big) * src[(size_t)s * RP + D + 1];
+  lsum = warp_sum(lsum);
   float acc[(D + 31) / 32];
 #pragma unroll
   for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+#pragma unroll 4
   for (int s = 0; s < n_splits; ++s) {
     const float w = exp2f(src[(size_t)s * RP + D] - big);
-    lsum += w * src[(size_t)s * RP + D + 1];
 #pragma unroll
     for (int i = 0; i < (D + 31) / 32; ++i) {
       const int d = lane + 32 * i;
@@ -421,14 +429,14 @@ KRK_API int krk_attention_decode(void* out, const void* qkv, int q_stride, int H
     configured = true;
   }
   dim3 grid(splits, HKV * row_tiles, n_seqs);
-  attention_decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>(
-      (float*)part, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, table, width, (const bf16*)k_cache,
-      (const bf16*)v_cache, scale * LOG2E, window, row_tiles);
-  KRK_CHECK_LAUNCH();
+  cudaError_t e = launch_pdl(attention_decode_kernel, grid, dim3(THREADS), DECODE_SMEM, stream, (float*)part,
+                             (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, table, width,
+                             (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window, row_tiles);
+  if (e != cudaSuccess) return (int)e;
   const int items = n_seqs * HQ;
-  attention_merge_kernel<<<(items + 3) / 4, 128, 0, stream>>>((bf16*)out, (const float*)part, items, splits);
-  KRK_CHECK_LAUNCH();
-  return 0;
+  e = launch_pdl(attention_merge_kernel, dim3((items + 3) / 4), dim3(128), 0, stream, (bf16*)out, (const float*)part,
+                 items, splits);
+  return (int)e;
 }
 
 #endif  // head size served by the tensor-core kernels

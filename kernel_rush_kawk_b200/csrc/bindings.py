@@ -41,7 +41,7 @@ _SIGNATURES = {
     "krk_qk_norm_rope_write": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int,
                                c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
-    "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P],
+    "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -75,6 +75,9 @@ class Kernels:
     libraries are needed (compiled at first use)."""
 
     SKINNY_MAX_ROWS = 16  # rows up to which the fused skinny kernels serve a bfloat16 product
+    # Every block of a skinny product redoes the norm of all rows in its prologue. That is
+    # cheaper than a separate norm kernel for one or two rows and dearer beyond.
+    FUSED_NORM_MAX_ROWS = 2
 
     def __init__(self, head_dims=(), device="cuda:0"):
         if not torch.cuda.is_available():
@@ -87,6 +90,7 @@ class Kernels:
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.has_skinny = hasattr(self.core, "krk_skinny_linear")
         self._partials: dict = {}
+        self._select_scratch = None
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -196,8 +200,10 @@ class Kernels:
     def _fits_prologue(x) -> bool:
         """Whether the normalised rows fit the fused kernel's shared memory."""
         rows, k = x.shape
+        if rows > Kernels.FUSED_NORM_MAX_ROWS:
+            return False
         tiles = 1 if rows <= 8 else 2
-        return 8 * tiles * (k + 64) * 2 + 8 * 2 * tiles * 512 <= 200 * 1024
+        return 65536 + 8 * tiles * (k + 64) * 2 + 8 * 2 * tiles * 512 <= 216 * 1024
 
     def _skinny_input(self, x):
         """A Normed goes to the kernel as it is if its norm is still to be done and fits
@@ -289,9 +295,11 @@ class Kernels:
         logits = logits.contiguous()
         f = (None, None, None) if feed is None else (feed.tokens.data_ptr(), feed.row_pos.data_ptr(),
                                                      feed.seq_start.data_ptr())
+        if self._select_scratch is None or self._select_scratch.numel() < n:
+            self._select_scratch = torch.zeros(max(n, 256), dtype=torch.int64, device=self.device)
         self._ok(self.core.krk_select_tokens(tokens.data_ptr(), logits.data_ptr(), n, vocab, temperature,
                                              seed & 0xFFFFFFFF, requests.data_ptr(), step & 0xFFFFFFFF, *f,
-                                             self._stream()), "token selection")
+                                             self._select_scratch.data_ptr(), self._stream()), "token selection")
         return tokens
 
 

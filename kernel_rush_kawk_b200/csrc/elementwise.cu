@@ -41,6 +41,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, T* x_new, const T* x, const 
                                const void* __restrict__ gain, int gain_f32, int H, float eps) {
   extern __shared__ float row_s[];  // H floats
   __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const size_t base = (size_t)blockIdx.x * H;
   float sq = 0.f;
   if (VEC) {
@@ -99,15 +101,17 @@ int launch_rmsnorm(void* out, void* x_new, const void* x, const void* branch, co
   const bool vec = (H % 4 == 0);
   auto kern = vec ? rmsnorm_kernel<T, true> : rmsnorm_kernel<T, false>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  kern<<<rows, threads, smem, stream>>>((T*)out, (T*)x_new, (const T*)x, (const T*)branch, gain, gain_f32, H, eps);
-  KRK_CHECK_LAUNCH();
-  return 0;
+  cudaError_t e = launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (T*)out, (T*)x_new, (const T*)x,
+                             (const T*)branch, gain, gain_f32, H, eps);
+  return (int)e;
 }
 
 // out[r] = table[ids[r]] ; an id outside [0, n_table_rows) sets *error and yields zeros.
 template <typename T>
 __global__ void gather_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids, int H,
                               int n_table_rows, int* error) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const int id = ids[r];
   const bool bad = id < 0 || id >= n_table_rows;
@@ -149,11 +153,10 @@ KRK_API int krk_gather_rows(void* out, const void* table, const int* ids, int ro
                             int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (dtype == KRK_DTYPE_F32)
-    gather_kernel<float><<<rows, 128, 0, stream>>>((float*)out, (const float*)table, ids, H, n_table_rows, error);
-  else
-    gather_kernel<bf16><<<rows, 128, 0, stream>>>((bf16*)out, (const bf16*)table, ids, H, n_table_rows, error);
-  KRK_CHECK_LAUNCH();
-  return 0;
+    return (int)launch_pdl(gather_kernel<float>, dim3(rows), dim3(128), 0, stream, (float*)out, (const float*)table, ids,
+                           H, n_table_rows, error);
+  return (int)launch_pdl(gather_kernel<bf16>, dim3(rows), dim3(128), 0, stream, (bf16*)out, (const bf16*)table, ids, H,
+                         n_table_rows, error);
 }
 
 KRK_API int krk_swiglu(void* out, const void* gu, int rows, int I, int dtype, cudaStream_t stream) {

@@ -21,6 +21,8 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const void* __res
                                           const int* __restrict__ table, int width, T* __restrict__ k_cache,
                                           T* __restrict__ v_cache, int rows, int HQ, int HKV, int D, float eps,
                                           int n_pos, int* error) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -91,13 +93,10 @@ KRK_API int krk_qk_norm_rope_write(void* qkv, const void* q_gain, const void* k_
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -3;
   if (dtype == KRK_DTYPE_F32)
-    qk_norm_rope_write_kernel<float><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+    return (int)launch_pdl(qk_norm_rope_write_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
         (float*)qkv, q_gain, k_gain, gain_f32, (const float*)cos_t, (const float*)sin_t, row_seq, row_pos, seq_slot,
         table, width, (float*)k_cache, (float*)v_cache, rows, HQ, HKV, D, eps, n_pos, error);
-  else
-    qk_norm_rope_write_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+  return (int)launch_pdl(qk_norm_rope_write_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
         (bf16*)qkv, q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, row_seq, row_pos, seq_slot, table,
         width, (bf16*)k_cache, (bf16*)v_cache, rows, HQ, HKV, D, eps, n_pos, error);
-  KRK_CHECK_LAUNCH();
-  return 0;
 }

@@ -20,69 +20,93 @@ __host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   return x;
 }
 
-__global__ void select_tokens_kernel(int* __restrict__ tokens, const float* __restrict__ logits, int vocab,
-                                     float temperature, uint32_t seed, const int* __restrict__ requests,
-                                     uint32_t step, int* __restrict__ feed_tokens, int* __restrict__ feed_pos,
-                                     int* __restrict__ feed_start) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
-  const int row = blockIdx.x;
+// Order-preserving map from float to unsigned: a < b  <=>  key(a) < key(b).
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Phase 1: block (chunk, row) scans its share of the row and folds its best (value,
+// index) into packed[row] with a 64-bit atomic max of (ordered value, ~index): the
+// maximum is the largest value and, among equals, the lowest index, in whatever order
+// the blocks arrive. packed[row] must be 0 on entry; phase 2 leaves it 0 again.
+__global__ void select_scan_kernel(unsigned long long* __restrict__ packed, const float* __restrict__ logits, int vocab,
+                                   float temperature, uint32_t seed, const int* __restrict__ requests, uint32_t step) {
+  __shared__ unsigned long long best_s[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.y;
   const float* x = logits + (size_t)row * vocab;
   const bool sample = temperature > 0.f;
   uint32_t key = 0;
   if (sample) key = mix32(mix32(mix32(seed) ^ (uint32_t)requests[row]) ^ step);
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  const int per = (vocab + gridDim.x - 1) / gridDim.x;
+  const int begin = blockIdx.x * per, end = min(vocab, begin + per);
+  unsigned long long best = 0;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
     float v = x[i];
     if (sample) {
       const uint32_t h = mix32(key ^ ((uint32_t)i * 0x9E3779B9u));
       const float u = ((float)(h >> 9) + 0.5f) * (1.0f / 8388608.0f);
       v = v / temperature - logf(-logf(u));
     }
-    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    const unsigned long long cand = ((unsigned long long)ordered_bits(v) << 32) | (uint32_t)(~(uint32_t)i);
+    best = cand > best ? cand : best;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  if (lane == 0) best_s[warp] = best;
   __syncthreads();
   if (warp == 0) {
-    const int n_warps = blockDim.x >> 5;
-    bv = lane < n_warps ? best_v[lane] : -INFINITY;
-    bi = lane < n_warps ? best_i[lane] : 0x7fffffff;
+    best = lane < (blockDim.x >> 5) ? best_s[lane] : 0ull;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
     }
-    if (lane == 0) {
-      const int tok = bi == 0x7fffffff ? 0 : bi;
-      tokens[row] = tok;
-      if (feed_tokens) {  // feed the next single-token step on the device: its token, its position
-        feed_tokens[row] = tok;
-        feed_pos[row] += 1;
-        feed_start[row] += 1;
-      }
-    }
+    if (lane == 0 && best) atomicMax(packed + row, best);
+  }
+}
+
+// Phase 2: one thread per row turns packed[row] into the token, optionally feeds the
+// next single-token step, and clears packed[row].
+__global__ void select_finish_kernel(int* __restrict__ tokens, unsigned long long* __restrict__ packed, int rows,
+                                     int* __restrict__ feed_tokens, int* __restrict__ feed_pos,
+                                     int* __restrict__ feed_start) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const unsigned long long best = packed[row];
+  packed[row] = 0ull;
+  const int tok = best ? (int)(~(uint32_t)(best & 0xffffffffull)) : 0;
+  tokens[row] = tok;
+  if (feed_tokens) {  // feed the next single-token step on the device: its token, its position
+    feed_tokens[row] = tok;
+    feed_pos[row] += 1;
+    feed_start[row] += 1;
   }
 }
 
 }  // namespace
 
+// packed: 64-bit scratch, one word per row, zero before the first call (each call leaves it zero).
 // feed_*: null, or the token / row position / sequence start arrays of a single-token step's batch
 // description, which then describe the next step: token = the selected one, positions + 1.
 KRK_API int krk_select_tokens(int* tokens, const float* logits, int rows, int vocab, float temperature, unsigned seed,
                               const int* requests, unsigned step, int* feed_tokens, int* feed_pos, int* feed_start,
-                              cudaStream_t stream) {
+                              void* packed, cudaStream_t stream) {
   if (rows == 0) return 0;
-  select_tokens_kernel<<<rows, 1024, 0, stream>>>(tokens, logits, vocab, temperature, seed, requests, step,
-                                                  feed_tokens, feed_pos, feed_start);
-  KRK_CHECK_LAUNCH();
-  return 0;
+  if (rows > 65535) return -3;
+  const int chunks = max(1, min(64, vocab / 2048));
+  cudaError_t e = launch_pdl(select_scan_kernel, dim3(chunks, rows), dim3(256), 0, stream, (unsigned long long*)packed,
+                             logits, vocab, temperature, (uint32_t)seed, requests, (uint32_t)step);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_pdl(select_finish_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, tokens,
+                 (unsigned long long*)packed, rows, feed_tokens, feed_pos, feed_start);
+  return (int)e;
 }

@@ -24,11 +24,18 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int CHUNK = 32;   // k values per fragment load
-constexpr int LOADS = 8;    // 16-row tile chunks in flight per warp
+constexpr int CHUNK = 32;        // k values per fragment load
+constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 bytes each)
 
-// NT: 8-row batch tiles (1 or 2). STREAMS: weight row tiles per block: 1, 2 (two
-// row tiles), or gate+up when SWIGLU.
+// NT: 8-row batch tiles (1 or 2). RT: 16-row weight tiles per block; with SWIGLU the
+// block streams RT gate tiles and RT up tiles.
+//
+// Weight bytes travel global -> shared memory with cp.async into a ring that is
+// private to each thread: a thread later reads back exactly the 16-byte pieces it
+// copied itself, so the ring needs no barrier, only cp.async.wait_group. The first
+// ring-full of copies is issued before anything else (before the wait on the
+// previous kernel, before the norm prologue), so the memory system is busy from the
+// block's first instruction.
 template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ W,
@@ -36,43 +43,126 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
               int M, int N, int K, float eps, int pitch) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int TILES = SWIGLU ? 2 * RT : RT;  // 16-row weight tiles this block streams
-  constexpr int UNROLL = LOADS / TILES;
-  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                      // [8*NT][pitch] when NORM
-  float* red = reinterpret_cast<float*>(smem_raw + (NORM ? (size_t)8 * NT * pitch * 2 : 0));  // [WARPS][TILES*NT*4*32]
+  constexpr int STAGES = RING_LOADS / TILES;
+  constexpr int XSLOTS = NORM ? 0 : NT;          // without the prologue the batch rows ride in the ring too
+  constexpr int SLOTS = TILES * 2 + XSLOTS;      // 16-byte pieces per thread and stage
+  constexpr size_t RING_BYTES = (size_t)STAGES * SLOTS * THREADS * 16;
+  uint4* ring = reinterpret_cast<uint4*>(smem_raw);                                 // [STAGES][SLOTS][THREADS]
+  float* red = reinterpret_cast<float*>(smem_raw + RING_BYTES);                       // [WARPS][TILES*NT*4*32]
+  constexpr size_t RED_BYTES = (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw + RING_BYTES + RED_BYTES);              // [8*NT][pitch] when NORM
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
 
+  // weight rows of this block's tiles, clamped so that edge tiles read valid memory
+  const int n0 = blockIdx.x * 16 * RT;
+  const bf16* wrow[TILES][2];
+#pragma unroll
+  for (int s = 0; s < TILES; ++s) {
+    const int tile_row = n0 + (s % RT) * 16 + (SWIGLU && s >= RT ? N : 0);
+    const int limit = (SWIGLU && s >= RT ? 2 * N : N) - 1;
+    wrow[s][0] = W + (size_t)min(tile_row + g, limit) * K + 8 * t;
+    wrow[s][1] = W + (size_t)min(tile_row + g + 8, limit) * K + 8 * t;
+  }
+  const int n_chunks = K / CHUNK;
+  const int per_warp = (n_chunks + WARPS - 1) / WARPS;
+  const int c_begin = warp * per_warp, c_end = min(n_chunks, c_begin + per_warp);
+  const int nc = max(0, c_end - c_begin);
+
+  // batch rows of the B fragments when they come from global memory (no prologue)
+  const bf16* xsrc[NT];
+  bool xok[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int m = 8 * j + g;
+    xok[j] = NORM || m < M;
+    xsrc[j] = x + (size_t)min(m, M - 1) * K + 8 * t;
+  }
+
+  auto issue_w = [&](int i) {  // weights of chunk i of this warp's slice into stage i % STAGES
+    if (i < nc) {
+      uint4* dst = ring + ((size_t)(i % STAGES) * SLOTS) * THREADS + threadIdx.x;
+      const size_t off = (size_t)(c_begin + i) * CHUNK;
+#pragma unroll
+      for (int s = 0; s < TILES; ++s) {
+        cp_async_16(dst + (s * 2 + 0) * THREADS, wrow[s][0] + off);
+        cp_async_16(dst + (s * 2 + 1) * THREADS, wrow[s][1] + off);
+      }
+    }
+  };
+  auto issue_x = [&](int i) {  // the batch rows' piece of chunk i (only without the prologue)
+    if (!NORM && i < nc) {
+      uint4* dst = ring + ((size_t)(i % STAGES) * SLOTS + TILES * 2) * THREADS + threadIdx.x;
+      const size_t off = (size_t)(c_begin + i) * CHUNK;
+#pragma unroll
+      for (int j = 0; j < XSLOTS; ++j)
+        if (xok[j]) cp_async_16(dst + j * THREADS, xsrc[j] + off);
+    }
+  };
+  // Weights are written by no kernel: their copies start before the wait on the previous
+  // kernel. Activations come from it: their copies start after the wait. One commit group
+  // per stage, empty or not, so that group counting stays simple.
+#pragma unroll
+  for (int i = 0; i < STAGES; ++i) issue_w(i);
+  grid_launch_dependents();
+  grid_dependency_wait();  // x, branch come from earlier kernels; x_new may still be read by them
+#pragma unroll
+  for (int i = 0; i < STAGES; ++i) {
+    issue_x(i);
+    cp_async_commit();
+  }
+
   if (NORM) {
-    // one warp per batch row: add, statistics, normalise, into shared memory
-    for (int m = warp; m < 8 * NT; m += WARPS) {
+    // All threads work on every batch row: thread c owns the 8-element pieces c, c + 256, ...
+    // of a row. Pass 1: s = round(x + branch) into shared memory, partial sums of squares per
+    // warp. Pass 2, after the warps' partials are added in warp order: normalise in place.
+    float* partial = red;  // [8*NT][WARPS]; the reduction buffer is free until the main loop ends
+    const int K8 = K / 8;
+    float sq[8 * NT];
+#pragma unroll
+    for (int m = 0; m < 8 * NT; ++m) sq[m] = 0.f;
+    for (int c = threadIdx.x; c < K8; c += THREADS) {
+      const int k = c * 8;
+      // the rows' loads are independent of one another: unrolled, they are all in flight together
+#pragma unroll
+      for (int m = 0; m < 8 * NT; ++m) {
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (m < M) {
+          xv = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
+          __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xv);
+          if (branch) {
+            uint4 bv = *reinterpret_cast<const uint4*>(branch + (size_t)m * K + k);
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              xp[j] = __floats2bfloat162_rn(__low2float(xp[j]) + __low2float(bp[j]),
+                                            __high2float(xp[j]) + __high2float(bp[j]));
+            if (blockIdx.x == 0) *reinterpret_cast<uint4*>(x_new + (size_t)m * K + k) = xv;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = __low2float(xp[j]), b = __high2float(xp[j]);
+            sq[m] += a * a + b * b;
+          }
+        }
+        *reinterpret_cast<uint4*>(xs + (size_t)m * pitch + k) = xv;
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < 8 * NT; ++m) {
+      const float v = warp_sum(sq[m]);
+      if (lane == 0) partial[m * WARPS + warp] = v;
+    }
+    __syncthreads();
+    for (int m = 0; m < M; ++m) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) total += partial[m * WARPS + w];
+      const float r = rsqrtf(total / (float)K + eps);
       bf16* dst = xs + (size_t)m * pitch;
-      if (m >= M) {
-        for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
-        continue;
-      }
-      float sq = 0.f;
-      for (int k = lane * 8; k < K; k += 256) {
-        uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
-        __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xv);
-        if (branch) {
-          uint4 bv = *reinterpret_cast<const uint4*>(branch + (size_t)m * K + k);
-          const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            xp[j] = __floats2bfloat162_rn(__low2float(xp[j]) + __low2float(bp[j]), __high2float(xp[j]) + __high2float(bp[j]));
-          if (blockIdx.x == 0) *reinterpret_cast<uint4*>(x_new + (size_t)m * K + k) = xv;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = __low2float(xp[j]), b = __high2float(xp[j]);
-          sq += a * a + b * b;
-        }
-        *reinterpret_cast<uint4*>(dst + k) = xv;
-      }
-      sq = warp_sum(sq);
-      const float r = rsqrtf(sq / (float)K + eps);
-      for (int k = lane * 8; k < K; k += 256) {
+      for (int c = threadIdx.x; c < K8; c += THREADS) {
+        const int k = c * 8;
         uint4 xv = *reinterpret_cast<uint4*>(dst + k);
         __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xv);
 #pragma unroll
@@ -87,25 +177,10 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
     __syncthreads();
   }
 
-  // weight rows of this block's tiles, clamped so that edge tiles read valid memory
-  const int n0 = blockIdx.x * 16 * RT;
-  const bf16* wrow[TILES][2];
-#pragma unroll
-  for (int s = 0; s < TILES; ++s) {
-    const int tile_row = n0 + (s % RT) * 16 + (SWIGLU && s >= RT ? N : 0);
-    const int limit = (SWIGLU && s >= RT ? 2 * N : N) - 1;
-    wrow[s][0] = W + (size_t)min(tile_row + g, limit) * K + 8 * t;
-    wrow[s][1] = W + (size_t)min(tile_row + g + 8, limit) * K + 8 * t;
-  }
-  // batch rows of the B fragments
+  // batch rows of the B fragments after the prologue: normalised rows in shared memory
   const bf16* xrow[NT];
-  bool xok[NT];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int m = 8 * j + g;
-    xok[j] = NORM || m < M;
-    xrow[j] = NORM ? xs + (size_t)m * pitch + 8 * t : x + (size_t)min(m, M - 1) * K + 8 * t;
-  }
+  for (int j = 0; j < NT; ++j) xrow[j] = xs + (size_t)(8 * j + g) * pitch + 8 * t;
 
   float acc[TILES][NT][4];
 #pragma unroll
@@ -115,38 +190,32 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[s][j][c] = 0.f;
 
-  const int n_chunks = K / CHUNK;
-  const int per_warp = (n_chunks + WARPS - 1) / WARPS;
-  const int c_begin = warp * per_warp, c_end = min(n_chunks, c_begin + per_warp);
-
-  for (int c0 = c_begin; c0 < c_end; c0 += UNROLL) {
-    uint4 wa[UNROLL][TILES][2];
+  for (int i = 0; i < nc; ++i) {
+    cp_async_wait<STAGES - 1>();  // all but the newest STAGES-1 groups are complete: chunk i has landed
+    const uint4* src = ring + ((size_t)(i % STAGES) * SLOTS) * THREADS + threadIdx.x;
+    uint4 wa[TILES][2];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int c = min(c0 + u, c_end - 1);  // a repeated chunk is loaded but not used
+    for (int s = 0; s < TILES; ++s) {
+      wa[s][0] = src[(s * 2 + 0) * THREADS];
+      wa[s][1] = src[(s * 2 + 1) * THREADS];
+    }
+    const int c = c_begin + i;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      uint4 xb = make_uint4(0, 0, 0, 0);
+      if (NORM) xb = *reinterpret_cast<const uint4*>(xrow[j] + (size_t)c * CHUNK);
+      else if (xok[j]) xb = src[(TILES * 2 + j) * THREADS];
 #pragma unroll
       for (int s = 0; s < TILES; ++s) {
-        wa[u][s][0] = ld_stream_16(wrow[s][0] + (size_t)c * CHUNK);
-        wa[u][s][1] = ld_stream_16(wrow[s][1] + (size_t)c * CHUNK);
+        mma_bf16_16816(acc[s][j], wa[s][0].x, wa[s][1].x, wa[s][0].y, wa[s][1].y, xb.x, xb.y);
+        mma_bf16_16816(acc[s][j], wa[s][0].z, wa[s][1].z, wa[s][0].w, wa[s][1].w, xb.z, xb.w);
       }
     }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (c0 + u < c_end) {
-        const int c = c0 + u;
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          uint4 xb = make_uint4(0, 0, 0, 0);
-          if (xok[j]) xb = *reinterpret_cast<const uint4*>(xrow[j] + (size_t)c * CHUNK);
-#pragma unroll
-          for (int s = 0; s < TILES; ++s) {
-            mma_bf16_16816(acc[s][j], wa[u][s][0].x, wa[u][s][1].x, wa[u][s][0].y, wa[u][s][1].y, xb.x, xb.y);
-            mma_bf16_16816(acc[s][j], wa[u][s][0].z, wa[u][s][1].z, wa[u][s][0].w, wa[u][s][1].w, xb.z, xb.w);
-          }
-        }
-      }
-    }
+    issue_w(i + STAGES);  // refill the stage just consumed (its values are in registers and used)
+    issue_x(i + STAGES);
+    cp_async_commit();
   }
+  cp_async_wait<0>();
 
   // reduce over the warps in a fixed order
   constexpr int PER_WARP = TILES * NT * 4 * 32;
@@ -187,20 +256,25 @@ template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
 int launch(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
   constexpr int TILES = SWIGLU ? 2 * RT : RT;
+  constexpr int STAGES = RING_LOADS / TILES;
   int pitch = 0;
-  size_t smem = (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
+  constexpr int SLOTS = TILES * 2 + (NORM ? 0 : NT);
+  size_t smem = (size_t)STAGES * SLOTS * THREADS * 16 + (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
   if (NORM) {
     const int pad_bytes = (64 - (K * 2) % 128 + 128) % 128;
     pitch = K + pad_bytes / 2;
     smem += (size_t)8 * NT * pitch * 2;
   }
-  if (smem > 200 * 1024) return -2;
+  if (smem > 220 * 1024) return -2;
   auto kern = skinny_kernel<NT, RT, SWIGLU, NORM, TOut>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
-  kern<<<blocks, THREADS, smem, stream>>>((TOut*)out, (const bf16*)x, (const bf16*)W, (const bf16*)branch, gain,
-                                          gain_f32, (bf16*)x_new, M, N, K, eps, pitch);
-  KRK_CHECK_LAUNCH();
+  cudaError_t e = launch_pdl(kern, dim3(blocks), dim3(THREADS), smem, stream, (TOut*)out, (const bf16*)x, (const bf16*)W,
+                             (const bf16*)branch, gain, gain_f32, (bf16*)x_new, M, N, K, eps, pitch);
+  if (e != cudaSuccess) return (int)e;
   return 0;
 }
 
