@@ -15,6 +15,8 @@
 // head; blocks are brought to shared memory with cp.async, two stages.
 //
 // Compiled once per head size: -DKRK_HEAD_DIM=<D>, D a multiple of 16 up to 256.
+#include <cooperative_groups.h>
+
 #include "mma.cuh"
 
 #ifndef KRK_HEAD_DIM
@@ -385,9 +387,248 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, const float* __re
   }
 }
 
+
+constexpr size_t FUSED_BASE_BYTES =
+    ((size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)5 * 16 * (D + 2) * sizeof(float))
+        ? (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)5 * 16 * (D + 2) * sizeof(float);
 constexpr size_t PAGE_SMEM = (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16);
 constexpr size_t RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t DECODE_SMEM = PAGE_SMEM > RED_SMEM ? PAGE_SMEM : RED_SMEM;
+
+// ---------------------------------------------------------------------------------
+// One token per sequence, everything between the QKV projection and the output
+// projection in one launch: per-head q/k RMSNorm and rotation of the new token
+// (rounding points of engine/kernels/rope.py:19-30 of the reference), the write of its
+// key and value to the cache, attention over the cache, and the merge of the key
+// splits. The splits of one (sequence, kv head, row tile) form a thread-block cluster;
+// each block leaves its partial (m, l, o[D]) in its own shared memory and block 0 of
+// the cluster reads the others' through distributed shared memory, so no partial
+// result goes through global memory and no second kernel merges.
+// ---------------------------------------------------------------------------------
+template <bool HAS_GAIN, bool HAS_ROPE>
+__device__ __forceinline__ void norm_rope_row(bf16* dst, const bf16* __restrict__ src, const void* gain, int gain_f32,
+                                              const bf16* __restrict__ cos_row, const bf16* __restrict__ sin_row,
+                                              float eps, int lane) {
+  constexpr int HALF = D / 2;
+  float sq = 0.f;
+  for (int i = lane; i < HALF; i += 32) {
+    const float a = __bfloat162float(src[i]), b = __bfloat162float(src[i + HALF]);
+    sq += a * a + b * b;
+  }
+  sq = warp_sum(sq);
+  const float r = rsqrtf(sq / (float)D + eps);
+  for (int i = lane; i < HALF; i += 32) {
+    float y1 = __bfloat162float(src[i]), y2 = __bfloat162float(src[i + HALF]);
+    if (HAS_GAIN) {
+      y1 = round_to<bf16>(load_gain<bf16>(gain, i, gain_f32) * round_to<bf16>(y1 * r));
+      y2 = round_to<bf16>(load_gain<bf16>(gain, i + HALF, gain_f32) * round_to<bf16>(y2 * r));
+    }
+    if (HAS_ROPE) {
+      const float c = __bfloat162float(cos_row[i]), s = __bfloat162float(sin_row[i]);
+      const float o1 = round_to<bf16>(y1 * c) + round_to<bf16>(-y2 * s);
+      const float o2 = round_to<bf16>(y2 * c) + round_to<bf16>(y1 * s);
+      y1 = o1;
+      y2 = o2;
+    }
+    dst[i] = __float2bfloat16_rn(y1);
+    dst[i + HALF] = __float2bfloat16_rn(y2);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
+                              const void* __restrict__ q_gain, const void* __restrict__ k_gain, int gain_f32,
+                              const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t, float eps,
+                              const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                              const int* __restrict__ table, int width, bf16* __restrict__ k_cache,
+                              bf16* __restrict__ v_cache, float scale_log2, int window, int row_tiles, int n_pos,
+                              int* __restrict__ error) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);                       // page buffers, later the partials
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw + FUSED_BASE_BYTES);          // [16][DP] rotated queries
+  bf16* kv_new = q_s + 16 * DP;                                         // [2][D] the new token's key and value
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int n_splits = cluster.num_blocks(), split = cluster.block_rank();
+  const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
+  const int seq = blockIdx.z;
+  const int G = HQ / HKV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  int pos = seq_start[seq];
+  const int slot = seq_slot[seq];
+  if (pos < 0 || pos >= n_pos) {  // flagged and clamped: never an access out of range
+    if (threadIdx.x == 0 && error) atomicExch(error, 2);
+    pos = max(0, min(pos, n_pos - 1));
+  }
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
+  const int n_blocks = j_last - j_first + 1;
+  const int per = (n_blocks + n_splits - 1) / n_splits;
+  const int j_lo = j_first + split * per, j_hi = min(j_last, j_lo + per - 1);
+  const bool owns_new = j_lo <= j_last && j_last <= j_hi;  // this block's keys include the new token's
+
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+  const size_t head_off = (size_t)kh * KRK_PAGE * D;
+  auto issue = [&](int j, int stage) {
+    const int page = table[(size_t)slot * width + j % width];
+    bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    load_page(ks, k_cache + (size_t)page * page_stride + head_off);
+    load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+    cp_async_commit();
+  };
+  if (j_lo <= j_hi) issue(j_lo, 0);  // the cache pages travel while the new token is prepared
+
+  // queries of this tile's heads: norm, rotation, into shared memory; rows beyond G are zero
+  const bf16* row = qkv + (size_t)seq * q_stride;
+  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
+  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
+  for (int r = warp; r < 16; r += 4) {
+    const int hr = rt * 16 + r;
+    bf16* dst = q_s + r * DP;
+    if (hr < G) {
+      const bf16* src = row + (size_t)(kh * G + hr) * D;
+      if (q_gain && cos_t) norm_rope_row<true, true>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
+      else if (q_gain) norm_rope_row<true, false>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
+      else if (cos_t) norm_rope_row<false, true>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
+      else norm_rope_row<false, false>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
+    } else {
+      for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16_rn(0.f);
+    }
+  }
+  // the new token's key and value: prepared by the block that will read them, written to the cache by it
+  if (owns_new && warp == 0) {
+    const bf16* ksrc = row + (size_t)(HQ + kh) * D;
+    const bf16* vsrc = row + (size_t)(HQ + HKV + kh) * D;
+    if (k_gain && cos_t) norm_rope_row<true, true>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
+    else if (k_gain) norm_rope_row<true, false>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
+    else if (cos_t) norm_rope_row<false, true>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
+    else norm_rope_row<false, false>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
+    for (int i = lane; i < D; i += 32) kv_new[D + i] = vsrc[i];
+    __syncwarp();
+    if (rt == 0) {
+      const int page = table[(size_t)slot * width + j_last % width];
+      const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
+      for (int i = lane; i < D; i += 32) {
+        k_cache[at + i] = kv_new[i];
+        v_cache[at + i] = kv_new[D + i];
+      }
+    }
+  }
+  __syncthreads();
+
+  uint32_t qf[KSTEPS][4];
+  load_q(qf, q_s + g * DP, q_s + (g + 8) * DP, lane);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  for (int j = j_lo; j <= j_hi; ++j) {
+    const int stage = (j - j_lo) & 1;
+    if (j + 1 <= j_hi) {
+      issue(j + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    bf16* vs = ks + TILE_ELEMS;
+    if (j == j_last) {  // the page in shared memory predates this step's write: put the new row in
+      for (int i = threadIdx.x; i < D; i += THREADS) {
+        ks[(pos % KRK_PAGE) * DP + i] = kv_new[i];
+        vs[(pos % KRK_PAGE) * DP + i] = kv_new[D + i];
+      }
+      __syncthreads();
+    }
+    const int key0 = warp * 16;
+    float s[2][4];
+    qk_tile<2>(s, qf, ks, key0, lane);
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = j * KRK_PAGE + key0 + n * 8 + 2 * t4 + (c & 1);
+        s[n][c] = (key <= pos && key >= lo) ? s[n][c] * scale_log2 : -INFINITY;
+      }
+    softmax_update<2>(s, m, l, o);
+    pv_tile<2>(o, s, vs, key0, lane);
+    __syncthreads();
+  }
+
+  // merge the four warps through shared memory, in warp order, into mine[16][D + 2]
+  constexpr int RP = D + 2;
+  float* red = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][RP]
+  float* mine = red + 4 * 16 * RP;                   // [16 rows][RP]: this block's partial
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float* dst = red + ((size_t)warp * 16 + g + 8 * h) * RP;
+    if (t4 == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n) {
+      dst[n * 8 + 2 * t4] = o[n][2 * h];
+      dst[n * 8 + 2 * t4 + 1] = o[n][2 * h + 1];
+    }
+  }
+  __syncthreads();
+  for (int r = warp; r < 16; r += 4) {
+    float mw[4], big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { mw[w] = red[((size_t)w * 16 + r) * RP + D]; big = fmaxf(big, mw[w]); }
+    const float safe = big == -INFINITY ? 0.f : big;
+    float wgt[4], lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
+    for (int d = lane; d < D; d += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+      mine[r * RP + d] = acc;
+    }
+    if (lane == 0) { mine[r * RP + D] = big; mine[r * RP + D + 1] = lsum; }
+  }
+  cluster.sync();  // every block's partial is in place
+  if (split == 0) {
+    for (int r = warp; r < 16; r += 4) {
+      const int hr = rt * 16 + r;
+      if (hr >= G) continue;
+      float big = -INFINITY;
+      for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, cluster.map_shared_rank(mine, s2)[r * RP + D]);
+      float lsum = 0.f;
+      float acc[(D + 31) / 32];
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+      for (int s2 = 0; s2 < n_splits; ++s2) {
+        const float* theirs = cluster.map_shared_rank(mine, s2);
+        const float w = exp2f(theirs[r * RP + D] - big);
+        lsum += w * theirs[r * RP + D + 1];
+#pragma unroll
+        for (int i = 0; i < (D + 31) / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) acc[i] += w * theirs[r * RP + d];
+        }
+      }
+      const float inv = 1.0f / lsum;
+      bf16* dst = out + ((size_t)seq * HQ + kh * G + hr) * D;
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+      }
+    }
+  }
+  cluster.sync();  // nobody leaves while block 0 still reads its shared memory
+}
+
+constexpr size_t FUSED_RED_SMEM = (size_t)5 * 16 * (D + 2) * sizeof(float);
+constexpr size_t FUSED_BASE = PAGE_SMEM > FUSED_RED_SMEM ? PAGE_SMEM : FUSED_RED_SMEM;
+constexpr size_t FUSED_SMEM = FUSED_BASE + (size_t)(16 * DP + 2 * D) * sizeof(bf16);
 
 }  // namespace
 
@@ -436,6 +677,47 @@ KRK_API int krk_attention_decode(void* out, const void* qkv, int q_stride, int H
   const int items = n_seqs * HQ;
   e = launch_pdl(attention_merge_kernel, dim3((items + 3) / 4), dim3(128), 0, stream, (bf16*)out, (const float*)part,
                  items, splits);
+  return (int)e;
+}
+
+// One token per sequence, from the raw QKV rows to the attention output in one launch (see the
+// kernel's text). qkv rows hold q heads, k heads, v heads; gains and tables may be null. splits:
+// 1, 2, 4 or 8 blocks per cluster. The keys and values of the new tokens are written to the cache.
+KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride, int HQ, int HKV, const void* q_gain,
+                                       const void* k_gain, int gain_f32, const void* cos_t, const void* sin_t,
+                                       float eps, const int* seq_slot, const int* seq_start, const int* table,
+                                       int width, void* k_cache, void* v_cache, int n_seqs, float scale, int window,
+                                       int splits, int n_pos, int* error, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  const int G = HQ / HKV;
+  const int row_tiles = (G + 15) / 16;
+  if (HKV * row_tiles > 65535 || n_seqs > 65535) return -3;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)FUSED_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, HKV * row_tiles, n_seqs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = FUSED_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = splits;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_fused_kernel, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV,
+                                     q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot,
+                                     seq_start, table, width, (bf16*)k_cache, (bf16*)v_cache, scale * LOG2E, window,
+                                     row_tiles, n_pos, error);
   return (int)e;
 }
 

@@ -51,6 +51,8 @@ _ATTN_SIGNATURES = {
                               c_int, _P],
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
+    "krk_attention_decode_fused": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
+                                   _P, c_int, c_float, c_int, c_int, c_int, _P, _P],
 }
 
 
@@ -241,6 +243,30 @@ class Kernels:
             cache.table.data_ptr(), cache.width, cache.k.data_ptr() if kv_in_row else None,
             cache.v.data_ptr() if kv_in_row else None, qkv.shape[0], heads, kv_in_row, head_dim, eps, n_pos,
             self.error.data_ptr(), _code(qkv.dtype), self._stream()), "q/k norm + rope + cache write")
+
+    def rope_attention(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache, scale,
+                       window):
+        """Per-head q/k norm, rotation, cache write and attention. A single-token step in
+        bfloat16 runs them as one kernel; everything else as two."""
+        lib = self._attn_lib(head_dim)
+        if (batch.is_decode and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and kv_in_row > 0
+                and hasattr(lib, "krk_attention_decode_fused") and qkv.shape[0] > 0):
+            n = batch.n_seqs
+            out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+            row_tiles = -(-(heads // cache.kv_heads) // 16)
+            want = -(-296 // (n * cache.kv_heads * row_tiles))
+            splits = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
+            gain = q_gain if q_gain is not None else k_gain
+            n_pos = cos.shape[0] if cos is not None else 0x7fffffff
+            self._ok(lib.krk_attention_decode_fused(
+                out.data_ptr(), qkv.data_ptr(), qkv.stride(0), heads, cache.kv_heads, _ptr(q_gain), _ptr(k_gain),
+                int(gain is not None and gain.dtype == torch.float32), _ptr(cos), _ptr(sin), eps,
+                batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
+                cache.k.data_ptr(), cache.v.data_ptr(), n, scale, int(window or 0), splits, n_pos,
+                self.error.data_ptr(), self._stream()), "fused decode attention")
+            return out
+        self.qk_norm_rope_write(qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache)
+        return self.attention(qkv, heads, kv_in_row, head_dim, batch, cache, scale, window)
 
     def attention(self, qkv, heads, kv_in_row, head_dim, batch, cache, scale, window):
         lib = self._attn_lib(head_dim)

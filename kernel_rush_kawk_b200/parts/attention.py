@@ -84,9 +84,8 @@ class GQAttention(Mixer):
         qkv = ops.linear(h, self.w_qkv)
         tables = self.position.rotary_tables() if self.position is not None else None
         cos, sin = tables if tables is not None else (None, None)
-        ops.qk_norm_rope_write(qkv, self.heads, kv_in_row, self.head_dim, self.q_gain, self.k_gain,
-                               self.eps, cos, sin, ctx.batch, cache)
-        attn = ops.attention(qkv, self.heads, kv_in_row, self.head_dim, ctx.batch, cache, self.scale, self.window)
+        attn = ops.rope_attention(qkv, self.heads, kv_in_row, self.head_dim, self.q_gain, self.k_gain, self.eps,
+                                  cos, sin, ctx.batch, cache, self.scale, self.window)
         return ops.linear(attn, self.w_o)
 
 

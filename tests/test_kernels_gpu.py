@@ -208,6 +208,41 @@ def test_rope_write_then_attention_prefill_and_decode(ops, dtype, shape, window)
         close(got, want, dtype, f"attention, step {s}, shape {shape}, window {window}")
 
 
+@pytest.mark.parametrize("shape", ATTN_SHAPES + [(40, 2, 64)])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("n_seqs", [1, 3, 40])
+def test_fused_decode_attention_against_the_two_kernel_path(ops, shape, window, n_seqs):
+    """Single-token steps in bfloat16: norm + rotation + cache write + attention + merge in
+    one launch, against the plain reference of each stage; 1, 3 and 40 sequences give
+    cluster sizes 8, 4 or 2, and 1."""
+    heads, kv_heads, D = shape
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    width = 6
+    cache = make_cache(n_seqs * width + 3, kv_heads, D, n_seqs, width, dtype, 70)
+    cache.window = window
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.k, ref_cache.v = cache.k.clone(), cache.v.clone()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    qg = (1.5 + 0.1 * rand((D,), torch.float32, 71)).to(dtype)
+    kg = (1.5 + 0.1 * rand((D,), torch.float32, 72)).to(dtype)
+    rnd = random.Random(5)
+    starts = [rnd.choice([0, 1, 63, 64, 127, 200, 383]) for _ in range(n_seqs)]
+    slots = list(range(n_seqs))
+    rnd.shuffle(slots)
+    batch = make_batch(slots, starts, [1] * n_seqs)
+    qkv = rand((n_seqs, (heads + 2 * kv_heads) * D), dtype, 73)
+    qkv_ref = qkv.clone()
+    scale = 1.0 / math.sqrt(D)
+    got = ops.rope_attention(qkv, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, cache, scale, window)
+    want = ref.rope_attention(qkv_ref, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, ref_cache, scale, window)
+    close(cache.k, ref_cache.k, dtype, "key pages after the fused step")
+    assert torch.equal(cache.v, ref_cache.v)
+    close(got, want, dtype, f"fused decode attention {shape} window {window} seqs {n_seqs}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_len", [1, 37])
 def test_one_far_key_among_hundreds_decides(ops, dtype, q_len):

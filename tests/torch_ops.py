@@ -103,6 +103,11 @@ class TorchOps:
             cache.k[page, :, off] = k
             cache.v[page, :, off] = v
 
+    def rope_attention(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache, scale,
+                       window):
+        self.qk_norm_rope_write(qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache)
+        return self.attention(qkv, heads, kv_in_row, head_dim, batch, cache, scale, window)
+
     def attention(self, qkv, heads, kv_in_row, head_dim, batch, cache, scale, window):
         D = head_dim
         rows = qkv.shape[0]
