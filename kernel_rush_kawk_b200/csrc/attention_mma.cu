@@ -17,6 +17,7 @@
 // Compiled once per head size: -DKRK_HEAD_DIM=<D>, D a multiple of 16 up to 256.
 #include <cooperative_groups.h>
 
+#define KRK_TRACE_OWNER  // with -DKRK_TRACE this file keeps a timeline buffer of its own
 #include "mma.cuh"
 
 #ifndef KRK_HEAD_DIM
@@ -389,8 +390,8 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, const float* __re
 
 
 constexpr size_t FUSED_BASE_BYTES =
-    ((size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)5 * 16 * (D + 2) * sizeof(float))
-        ? (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)5 * 16 * (D + 2) * sizeof(float);
+    ((size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)4 * 16 * (D + 2) * sizeof(float))
+        ? (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t PAGE_SMEM = (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16);
 constexpr size_t RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t DECODE_SMEM = PAGE_SMEM > RED_SMEM ? PAGE_SMEM : RED_SMEM;
@@ -405,35 +406,57 @@ constexpr size_t DECODE_SMEM = PAGE_SMEM > RED_SMEM ? PAGE_SMEM : RED_SMEM;
 // the cluster reads the others' through distributed shared memory, so no partial
 // result goes through global memory and no second kernel merges.
 // ---------------------------------------------------------------------------------
-template <bool HAS_GAIN, bool HAS_ROPE>
-__device__ __forceinline__ void norm_rope_row(bf16* dst, const bf16* __restrict__ src, const void* gain, int gain_f32,
-                                              const bf16* __restrict__ cos_row, const bf16* __restrict__ sin_row,
-                                              float eps, int lane) {
-  constexpr int HALF = D / 2;
-  float sq = 0.f;
-  for (int i = lane; i < HALF; i += 32) {
-    const float a = __bfloat162float(src[i]), b = __bfloat162float(src[i + HALF]);
-    sq += a * a + b * b;
-  }
-  sq = warp_sum(sq);
-  const float r = rsqrtf(sq / (float)D + eps);
-  for (int i = lane; i < HALF; i += 32) {
-    float y1 = __bfloat162float(src[i]), y2 = __bfloat162float(src[i + HALF]);
-    if (HAS_GAIN) {
-      y1 = round_to<bf16>(load_gain<bf16>(gain, i, gain_f32) * round_to<bf16>(y1 * r));
-      y2 = round_to<bf16>(load_gain<bf16>(gain, i + HALF, gain_f32) * round_to<bf16>(y2 * r));
+// One head row of the new token: its values, gains and table entries are loaded first,
+// all at once, and the arithmetic follows, so that a row costs one memory latency.
+// Lane L owns the pairs (i, i + D/2) for i = L, L + 32, ...
+struct HeadRow {
+  static constexpr int PAIRS = (D / 2 + 31) / 32;
+  float lo[PAIRS], hi[PAIRS], g_lo[PAIRS], g_hi[PAIRS], c[PAIRS], s[PAIRS];
+
+  __device__ __forceinline__ void load(const bf16* __restrict__ src, const void* gain, int gain_f32,
+                                       const bf16* __restrict__ cos_row, const bf16* __restrict__ sin_row, int lane) {
+    constexpr int HALF = D / 2;
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int i = lane + 32 * p;
+      const bool ok = i < HALF;
+      lo[p] = ok ? __bfloat162float(src[i]) : 0.f;
+      hi[p] = ok ? __bfloat162float(src[i + HALF]) : 0.f;
+      g_lo[p] = (ok && gain) ? load_gain<bf16>(gain, i, gain_f32) : 1.f;
+      g_hi[p] = (ok && gain) ? load_gain<bf16>(gain, i + HALF, gain_f32) : 1.f;
+      c[p] = (ok && cos_row) ? __bfloat162float(cos_row[i]) : 1.f;
+      s[p] = (ok && sin_row) ? __bfloat162float(sin_row[i]) : 0.f;
     }
-    if (HAS_ROPE) {
-      const float c = __bfloat162float(cos_row[i]), s = __bfloat162float(sin_row[i]);
-      const float o1 = round_to<bf16>(y1 * c) + round_to<bf16>(-y2 * s);
-      const float o2 = round_to<bf16>(y2 * c) + round_to<bf16>(y1 * s);
-      y1 = o1;
-      y2 = o2;
-    }
-    dst[i] = __float2bfloat16_rn(y1);
-    dst[i + HALF] = __float2bfloat16_rn(y2);
   }
-}
+
+  // norm (if has_gain), rotation (if has_rope), rounded as the reference rounds; written to dst
+  __device__ __forceinline__ void finish(bf16* dst, bool has_gain, bool has_rope, float eps, int lane) const {
+    constexpr int HALF = D / 2;
+    float sq = 0.f;
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) sq += lo[p] * lo[p] + hi[p] * hi[p];
+    sq = warp_sum(sq);
+    const float r = rsqrtf(sq / (float)D + eps);
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int i = lane + 32 * p;
+      if (i >= HALF) continue;
+      float y1 = lo[p], y2 = hi[p];
+      if (has_gain) {
+        y1 = round_to<bf16>(g_lo[p] * round_to<bf16>(y1 * r));
+        y2 = round_to<bf16>(g_hi[p] * round_to<bf16>(y2 * r));
+      }
+      if (has_rope) {
+        const float o1 = round_to<bf16>(y1 * c[p]) + round_to<bf16>(-y2 * s[p]);
+        const float o2 = round_to<bf16>(y2 * c[p]) + round_to<bf16>(y1 * s[p]);
+        y1 = o1;
+        y2 = o2;
+      }
+      dst[i] = __float2bfloat16_rn(y1);
+      dst[i + HALF] = __float2bfloat16_rn(y2);
+    }
+  }
+};
 
 __global__ void __launch_bounds__(THREADS)
 attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
@@ -442,15 +465,20 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
                               const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                               const int* __restrict__ table, int width, bf16* __restrict__ k_cache,
                               bf16* __restrict__ v_cache, float scale_log2, int window, int row_tiles, int n_pos,
-                              int* __restrict__ error) {
+                              int inbox_rows, int* __restrict__ error) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);                       // page buffers, later the partials
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw + FUSED_BASE_BYTES);          // [16][DP] rotated queries
   bf16* kv_new = q_s + 16 * DP;                                         // [2][D] the new token's key and value
+  float* inbox = reinterpret_cast<float*>(kv_new + 2 * D);              // [splits][inbox_rows][D + 2], used in block 0
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
+  KRK_TRACE_DECL
+  // "I have started": waited for only before the first write into another block's shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   grid_launch_dependents();
   grid_dependency_wait();
+  KRK_TRACE_READY
   const int n_splits = cluster.num_blocks(), split = cluster.block_rank();
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
   const int seq = blockIdx.z;
@@ -481,39 +509,58 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   };
   if (j_lo <= j_hi) issue(j_lo, 0);  // the cache pages travel while the new token is prepared
 
-  // queries of this tile's heads: norm, rotation, into shared memory; rows beyond G are zero
+  // The new token: queries of this tile's heads (rows beyond G are zero) and, in the block
+  // whose keys include it, its key and value. Warp w takes rows w, w + 4, ...; the key row
+  // goes to the warp after the last query row. Every row's loads are issued before any
+  // arithmetic, so the warps pay one memory latency, not one per row.
   const bf16* row = qkv + (size_t)seq * q_stride;
   const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
   const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
-  for (int r = warp; r < 16; r += 4) {
-    const int hr = rt * 16 + r;
-    bf16* dst = q_s + r * DP;
-    if (hr < G) {
-      const bf16* src = row + (size_t)(kh * G + hr) * D;
-      if (q_gain && cos_t) norm_rope_row<true, true>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
-      else if (q_gain) norm_rope_row<true, false>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
-      else if (cos_t) norm_rope_row<false, true>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
-      else norm_rope_row<false, false>(dst, src, q_gain, gain_f32, cos_row, sin_row, eps, lane);
-    } else {
-      for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16_rn(0.f);
+  const int q_rows = min(16, G - rt * 16);
+  const int k_warp = q_rows % 4;  // the warp with the fewest query rows
+  {
+    constexpr int MAX_ROWS = 4;  // 16 rows over 4 warps
+    HeadRow regs[MAX_ROWS];
+    HeadRow k_regs;
+    float v_regs[(D + 31) / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_ROWS; ++i) {
+      const int r = warp + 4 * i;
+      if (r < q_rows) regs[i].load(row + (size_t)(kh * G + rt * 16 + r) * D, q_gain, gain_f32, cos_row, sin_row, lane);
     }
-  }
-  // the new token's key and value: prepared by the block that will read them, written to the cache by it
-  if (owns_new && warp == 0) {
-    const bf16* ksrc = row + (size_t)(HQ + kh) * D;
-    const bf16* vsrc = row + (size_t)(HQ + HKV + kh) * D;
-    if (k_gain && cos_t) norm_rope_row<true, true>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
-    else if (k_gain) norm_rope_row<true, false>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
-    else if (cos_t) norm_rope_row<false, true>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
-    else norm_rope_row<false, false>(kv_new, ksrc, k_gain, gain_f32, cos_row, sin_row, eps, lane);
-    for (int i = lane; i < D; i += 32) kv_new[D + i] = vsrc[i];
-    __syncwarp();
-    if (rt == 0) {
-      const int page = table[(size_t)slot * width + j_last % width];
-      const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
-      for (int i = lane; i < D; i += 32) {
-        k_cache[at + i] = kv_new[i];
-        v_cache[at + i] = kv_new[D + i];
+    const bool do_k = owns_new && warp == k_warp;
+    if (do_k) {
+      k_regs.load(row + (size_t)(HQ + kh) * D, k_gain, gain_f32, cos_row, sin_row, lane);
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        v_regs[i] = d < D ? __bfloat162float(row[(size_t)(HQ + HKV + kh) * D + d]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_ROWS; ++i) {
+      const int r = warp + 4 * i;
+      if (r < q_rows) {
+        regs[i].finish(q_s + r * DP, q_gain != nullptr, cos_t != nullptr, eps, lane);
+      } else if (r < 16) {
+        for (int d = lane; d < D; d += 32) q_s[r * DP + d] = __float2bfloat16_rn(0.f);
+      }
+    }
+    if (do_k) {
+      k_regs.finish(kv_new, k_gain != nullptr, cos_t != nullptr, eps, lane);
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) kv_new[D + d] = __float2bfloat16_rn(v_regs[i]);
+      }
+      __syncwarp();
+      if (rt == 0) {
+        const int page = table[(size_t)slot * width + j_last % width];
+        const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
+        for (int d = lane; d < D; d += 32) {
+          k_cache[at + d] = kv_new[d];
+          v_cache[at + d] = kv_new[D + d];
+        }
       }
     }
   }
@@ -521,6 +568,10 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
 
   uint32_t qf[KSTEPS][4];
   load_q(qf, q_s + g * DP, q_s + (g + 8) * DP, lane);
+  KRK_TRACE_END(1)
+#ifdef KRK_TRACE
+  t_begin__ = krk_now();
+#endif
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[DTILES][4];
@@ -562,10 +613,13 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     __syncthreads();
   }
 
-  // merge the four warps through shared memory, in warp order, into mine[16][D + 2]
+  // Merge the four warps through shared memory, in warp order, and push the block's partial
+  // (m, l, o[D]) per row straight into block 0's inbox through distributed shared memory.
+  // One cluster barrier later block 0 holds every split's partial locally and merges them in
+  // split order; the other blocks are done.
   constexpr int RP = D + 2;
-  float* red = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][RP]
-  float* mine = red + 4 * 16 * RP;                   // [16 rows][RP]: this block's partial
+  float* red = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][RP]; the page buffers are free now
+  float* inbox0 = cluster.map_shared_rank(inbox, 0);  // [splits][inbox_rows][RP] in block 0
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float* dst = red + ((size_t)warp * 16 + g + 8 * h) * RP;
@@ -577,7 +631,8 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     }
   }
   __syncthreads();
-  for (int r = warp; r < 16; r += 4) {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block of the cluster has started
+  for (int r = warp; r < q_rows; r += 4) {
     float mw[4], big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) { mw[w] = red[((size_t)w * 16 + r) * RP + D]; big = fmaxf(big, mw[w]); }
@@ -585,37 +640,38 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     float wgt[4], lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
+    float* dst = inbox0 + ((size_t)split * inbox_rows + r) * RP;
     for (int d = lane; d < D; d += 32) {
       float acc = 0.f;
 #pragma unroll
       for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
-      mine[r * RP + d] = acc;
+      dst[d] = acc;
     }
-    if (lane == 0) { mine[r * RP + D] = big; mine[r * RP + D + 1] = lsum; }
+    if (lane == 0) { dst[D] = big; dst[D + 1] = lsum; }
   }
-  cluster.sync();  // every block's partial is in place
+  KRK_TRACE_READY
+  cluster.sync();  // every block's partial has arrived in block 0
   if (split == 0) {
-    for (int r = warp; r < 16; r += 4) {
-      const int hr = rt * 16 + r;
-      if (hr >= G) continue;
+    for (int r = warp; r < q_rows; r += 4) {
+      const float* mine = inbox + (size_t)r * RP;
+      const size_t step = (size_t)inbox_rows * RP;
       float big = -INFINITY;
-      for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, cluster.map_shared_rank(mine, s2)[r * RP + D]);
+      for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, mine[s2 * step + D]);
       float lsum = 0.f;
       float acc[(D + 31) / 32];
 #pragma unroll
       for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
       for (int s2 = 0; s2 < n_splits; ++s2) {
-        const float* theirs = cluster.map_shared_rank(mine, s2);
-        const float w = exp2f(theirs[r * RP + D] - big);
-        lsum += w * theirs[r * RP + D + 1];
+        const float w = exp2f(mine[s2 * step + D] - big);
+        lsum += w * mine[s2 * step + D + 1];
 #pragma unroll
         for (int i = 0; i < (D + 31) / 32; ++i) {
           const int d = lane + 32 * i;
-          if (d < D) acc[i] += w * theirs[r * RP + d];
+          if (d < D) acc[i] += w * mine[s2 * step + d];
         }
       }
       const float inv = 1.0f / lsum;
-      bf16* dst = out + ((size_t)seq * HQ + kh * G + hr) * D;
+      bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
 #pragma unroll
       for (int i = 0; i < (D + 31) / 32; ++i) {
         const int d = lane + 32 * i;
@@ -623,10 +679,10 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
       }
     }
   }
-  cluster.sync();  // nobody leaves while block 0 still reads its shared memory
+  KRK_TRACE_END(2)
 }
 
-constexpr size_t FUSED_RED_SMEM = (size_t)5 * 16 * (D + 2) * sizeof(float);
+constexpr size_t FUSED_RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t FUSED_BASE = PAGE_SMEM > FUSED_RED_SMEM ? PAGE_SMEM : FUSED_RED_SMEM;
 constexpr size_t FUSED_SMEM = FUSED_BASE + (size_t)(16 * DP + 2 * D) * sizeof(bf16);
 
@@ -680,6 +736,19 @@ KRK_API int krk_attention_decode(void* out, const void* qkv, int q_stride, int H
   return (int)e;
 }
 
+#ifdef KRK_TRACE
+KRK_API int krk_trace_dump(unsigned long long* host, unsigned int cap, unsigned int* count) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(count, krk_trace_count, sizeof(unsigned int));
+  unsigned int n = *count < cap ? *count : cap;
+  if (n > KRK_TRACE_CAP) n = KRK_TRACE_CAP;
+  cudaMemcpyFromSymbol(host, krk_trace_buf, (size_t)n * 4 * sizeof(unsigned long long));
+  unsigned int zero = 0;
+  cudaMemcpyToSymbol(krk_trace_count, &zero, sizeof(unsigned int));
+  return 0;
+}
+#endif
+
 // One token per sequence, from the raw QKV rows to the attention output in one launch (see the
 // kernel's text). qkv rows hold q heads, k heads, v heads; gains and tables may be null. splits:
 // 1, 2, 4 or 8 blocks per cluster. The keys and values of the new tokens are written to the cache.
@@ -693,17 +762,20 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
   const int row_tiles = (G + 15) / 16;
   if (HKV * row_tiles > 65535 || n_seqs > 65535) return -3;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -2;
-  static bool configured = false;
-  if (!configured) {
+  const int inbox_rows = G < 16 ? G : 16;
+  const size_t smem = FUSED_SMEM + (size_t)splits * inbox_rows * (D + 2) * sizeof(float);
+  if (smem > 220 * 1024) return -2;
+  static size_t configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)FUSED_SMEM);
+                                         (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, HKV * row_tiles, n_seqs);
   cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = FUSED_SMEM;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -717,7 +789,7 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
   cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_fused_kernel, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV,
                                      q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot,
                                      seq_start, table, width, (bf16*)k_cache, (bf16*)v_cache, scale * LOG2E, window,
-                                     row_tiles, n_pos, error);
+                                     row_tiles, n_pos, inbox_rows, error);
   return (int)e;
 }
 

@@ -205,7 +205,7 @@ class Kernels:
         if rows > Kernels.FUSED_NORM_MAX_ROWS:
             return False
         tiles = 1 if rows <= 8 else 2
-        return 65536 + 8 * tiles * (k + 64) * 2 + 8 * 2 * tiles * 512 <= 216 * 1024
+        return 65536 + rows * (k + 64) * 2 + 8 * 2 * tiles * 512 <= 216 * 1024
 
     def _skinny_input(self, x):
         """A Normed goes to the kernel as it is if its norm is still to be done and fits

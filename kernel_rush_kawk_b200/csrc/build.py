@@ -32,6 +32,8 @@ HEADERS = ["common.cuh", "mma.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# extra flags for performance work, e.g. KRK_EXTRA_NVCC_FLAGS="-DKRK_TRACE"; they are part of the library's hash
+NVCC_FLAGS += os.environ.get("KRK_EXTRA_NVCC_FLAGS", "").split()
 
 
 class BuildError(RuntimeError):

@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define KRK_PAGE 64  // cache positions per page
 
@@ -36,6 +37,35 @@ typedef __nv_bfloat16 bf16;
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Optional timeline for performance work (compile with -DKRK_TRACE): blocks record global
+// timer stamps into a buffer of the library that krk_trace_dump copies out.
+#if defined(KRK_TRACE) && defined(KRK_TRACE_OWNER)
+#define KRK_TRACE_CAP (1 << 20)
+static __device__ unsigned long long krk_trace_buf[KRK_TRACE_CAP * 4];
+static __device__ unsigned int krk_trace_count;
+__device__ __forceinline__ unsigned long long krk_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define KRK_TRACE_DECL unsigned long long t_begin__ = krk_now(), t_ready__ = 0;
+#define KRK_TRACE_READY t_ready__ = krk_now();
+#define KRK_TRACE_END(kind)                                                  \
+  if (threadIdx.x == 0) {                                                    \
+    unsigned int i__ = atomicAdd(&krk_trace_count, 1u);                      \
+    if (i__ < KRK_TRACE_CAP) {                                               \
+      krk_trace_buf[4 * i__] = ((unsigned long long)(kind) << 32) | blockIdx.x; \
+      krk_trace_buf[4 * i__ + 1] = t_begin__;                                \
+      krk_trace_buf[4 * i__ + 2] = t_ready__;                                \
+      krk_trace_buf[4 * i__ + 3] = krk_now();                                \
+    }                                                                        \
+  }
+#else
+#define KRK_TRACE_DECL
+#define KRK_TRACE_READY
+#define KRK_TRACE_END(kind)
+#endif
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {
@@ -47,8 +77,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  static const bool plain = getenv("KRK_NO_PDL") != nullptr;  // measurement switch: ordinary stream order
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = plain ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -18,12 +18,11 @@
 // reference's fused kernels compute it (gemm.py:22-51). Epilogue (swiglu): rows
 // n and N + n of W are gate and up; out = round(round(silu(round(g))) * round(u))
 // (gemm.py:108-113).
+#define KRK_TRACE_OWNER  // with -DKRK_TRACE this file keeps the timeline buffer
 #include "mma.cuh"
 
 namespace {
 
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
 constexpr int CHUNK = 32;        // k values per fragment load
 constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 bytes each)
 
@@ -36,12 +35,14 @@ constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 
 // ring-full of copies is issued before anything else (before the wait on the
 // previous kernel, before the norm prologue), so the memory system is busy from the
 // block's first instruction.
-template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
-__global__ void __launch_bounds__(THREADS)
+template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32)
 skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ W,
               const bf16* __restrict__ branch, const void* __restrict__ gain, int gain_f32, bf16* __restrict__ x_new,
               int M, int N, int K, float eps, int pitch) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  KRK_TRACE_DECL
+  constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;  // 16-row weight tiles this block streams
   constexpr int STAGES = RING_LOADS / TILES;
   constexpr int XSLOTS = NORM ? 0 : NT;          // without the prologue the batch rows ride in the ring too
@@ -50,7 +51,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   uint4* ring = reinterpret_cast<uint4*>(smem_raw);                                 // [STAGES][SLOTS][THREADS]
   float* red = reinterpret_cast<float*>(smem_raw + RING_BYTES);                       // [WARPS][TILES*NT*4*32]
   constexpr size_t RED_BYTES = (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
-  bf16* xs = reinterpret_cast<bf16*>(smem_raw + RING_BYTES + RED_BYTES);              // [8*NT][pitch] when NORM
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw + RING_BYTES + RED_BYTES);              // [M][pitch] when NORM
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -76,7 +77,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
     const int m = 8 * j + g;
-    xok[j] = NORM || m < M;
+    xok[j] = m < M;
     xsrc[j] = x + (size_t)min(m, M - 1) * K + 8 * t;
   }
 
@@ -107,6 +108,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   for (int i = 0; i < STAGES; ++i) issue_w(i);
   grid_launch_dependents();
   grid_dependency_wait();  // x, branch come from earlier kernels; x_new may still be read by them
+  KRK_TRACE_READY
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) {
     issue_x(i);
@@ -127,9 +129,8 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
       // the rows' loads are independent of one another: unrolled, they are all in flight together
 #pragma unroll
       for (int m = 0; m < 8 * NT; ++m) {
-        uint4 xv = make_uint4(0, 0, 0, 0);
         if (m < M) {
-          xv = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
+          uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k);
           __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xv);
           if (branch) {
             uint4 bv = *reinterpret_cast<const uint4*>(branch + (size_t)m * K + k);
@@ -145,8 +146,8 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
             const float a = __low2float(xp[j]), b = __high2float(xp[j]);
             sq[m] += a * a + b * b;
           }
+          *reinterpret_cast<uint4*>(xs + (size_t)m * pitch + k) = xv;
         }
-        *reinterpret_cast<uint4*>(xs + (size_t)m * pitch + k) = xv;
       }
     }
 #pragma unroll
@@ -203,7 +204,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       uint4 xb = make_uint4(0, 0, 0, 0);
-      if (NORM) xb = *reinterpret_cast<const uint4*>(xrow[j] + (size_t)c * CHUNK);
+      if (NORM) { if (xok[j]) xb = *reinterpret_cast<const uint4*>(xrow[j] + (size_t)c * CHUNK); }
       else if (xok[j]) xb = src[(TILES * 2 + j) * THREADS];
 #pragma unroll
       for (int s = 0; s < TILES; ++s) {
@@ -250,11 +251,13 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
       out[(size_t)m * N + n] = from_float<TOut>(v);
     }
   }
+  KRK_TRACE_END(K)
 }
 
-template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
-int launch(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
+template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
+int launch_warps(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
+  constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;
   constexpr int STAGES = RING_LOADS / TILES;
   int pitch = 0;
@@ -263,10 +266,10 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
   if (NORM) {
     const int pad_bytes = (64 - (K * 2) % 128 + 128) % 128;
     pitch = K + pad_bytes / 2;
-    smem += (size_t)8 * NT * pitch * 2;
+    smem += (size_t)M * pitch * 2;
   }
   if (smem > 220 * 1024) return -2;
-  auto kern = skinny_kernel<NT, RT, SWIGLU, NORM, TOut>;
+  auto kern = skinny_kernel<WARPS, NT, RT, SWIGLU, NORM, TOut>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -276,6 +279,18 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
                              (const bf16*)branch, gain, gain_f32, (bf16*)x_new, M, N, K, eps, pitch);
   if (e != cudaSuccess) return (int)e;
   return 0;
+}
+
+// Blocks of 8 warps hold more bytes in flight each; blocks of 4 warps are small enough for
+// five of them to share an SM. With between two and five blocks per SM the small ones all
+// fit at once (one wave, no straggling second wave of a few blocks); otherwise the large.
+template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
+int launch(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
+           int N, int K, float eps, cudaStream_t stream) {
+  const int blocks = (N + 16 * RT - 1) / (16 * RT);
+  if (blocks > 2 * 148 && blocks <= 5 * 148)
+    return launch_warps<4, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  return launch_warps<8, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
 }
 
 template <int NT, bool SWIGLU, bool NORM, typename TOut>
@@ -295,6 +310,19 @@ int pick_nt(void* out, const void* x, const void* W, const void* branch, const v
 }
 
 }  // namespace
+
+#ifdef KRK_TRACE
+KRK_API int krk_trace_dump(unsigned long long* host, unsigned int cap, unsigned int* count) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(count, krk_trace_count, sizeof(unsigned int));
+  unsigned int n = *count < cap ? *count : cap;
+  if (n > KRK_TRACE_CAP) n = KRK_TRACE_CAP;
+  cudaMemcpyFromSymbol(host, krk_trace_buf, (size_t)n * 4 * sizeof(unsigned long long));
+  unsigned int zero = 0;
+  cudaMemcpyToSymbol(krk_trace_count, &zero, sizeof(unsigned int));
+  return 0;
+}
+#endif
 
 // out [M, N] (bfloat16 or float32), x [M, K] bfloat16 contiguous, W [N, K] ([2N, K] with swiglu) bfloat16
 // contiguous; branch, gain, x_new may be null (see the file text). Needs M <= 16 and K % 32 == 0.
