@@ -413,8 +413,8 @@ struct HeadRow {
   static constexpr int PAIRS = (D / 2 + 31) / 32;
   float lo[PAIRS], hi[PAIRS], g_lo[PAIRS], g_hi[PAIRS], c[PAIRS], s[PAIRS];
 
-  __device__ __forceinline__ void load(const bf16* __restrict__ src, const void* gain, int gain_f32,
-                                       const bf16* __restrict__ cos_row, const bf16* __restrict__ sin_row, int lane) {
+  // the row's values and gains: their addresses do not depend on the token's position
+  __device__ __forceinline__ void load_values(const bf16* __restrict__ src, const void* gain, int gain_f32, int lane) {
     constexpr int HALF = D / 2;
 #pragma unroll
     for (int p = 0; p < PAIRS; ++p) {
@@ -424,6 +424,15 @@ struct HeadRow {
       hi[p] = ok ? __bfloat162float(src[i + HALF]) : 0.f;
       g_lo[p] = (ok && gain) ? load_gain<bf16>(gain, i, gain_f32) : 1.f;
       g_hi[p] = (ok && gain) ? load_gain<bf16>(gain, i + HALF, gain_f32) : 1.f;
+    }
+  }
+  // the rotation's table row of the token's position
+  __device__ __forceinline__ void load_angles(const bf16* __restrict__ cos_row, const bf16* __restrict__ sin_row, int lane) {
+    constexpr int HALF = D / 2;
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int i = lane + 32 * p;
+      const bool ok = i < HALF;
       c[p] = (ok && cos_row) ? __bfloat162float(cos_row[i]) : 1.f;
       s[p] = (ok && sin_row) ? __bfloat162float(sin_row[i]) : 0.f;
     }
@@ -487,10 +496,45 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   const int g = lane >> 2, t4 = lane & 3;
   int pos = seq_start[seq];
   const int slot = seq_slot[seq];
+
+  // The new token's rows. Warp w takes query rows w, w + 4, ... of this tile (rows beyond G
+  // are zero); the key and value rows go to the warp with the fewest query rows, in every
+  // block (only the block whose keys include the new token uses them). All loads whose
+  // addresses do not need the position are issued before the position is first used, and
+  // all loads of a row before any arithmetic: the prologue costs about two memory
+  // latencies, whatever the number of rows.
+  const bf16* row = qkv + (size_t)seq * q_stride;
+  const int q_rows = min(16, G - rt * 16);
+  const int k_warp = q_rows % 4;
+  constexpr int MAX_ROWS = 4;  // 16 rows over 4 warps
+  HeadRow regs[MAX_ROWS];
+  HeadRow k_regs;
+  float v_regs[(D + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i) {
+    const int r = warp + 4 * i;
+    if (r < q_rows) regs[i].load_values(row + (size_t)(kh * G + rt * 16 + r) * D, q_gain, gain_f32, lane);
+  }
+  if (warp == k_warp) {
+    k_regs.load_values(row + (size_t)(HQ + kh) * D, k_gain, gain_f32, lane);
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      v_regs[i] = d < D ? __bfloat162float(row[(size_t)(HQ + HKV + kh) * D + d]) : 0.f;
+    }
+  }
+
   if (pos < 0 || pos >= n_pos) {  // flagged and clamped: never an access out of range
     if (threadIdx.x == 0 && error) atomicExch(error, 2);
     pos = max(0, min(pos, n_pos - 1));
   }
+  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
+  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i)
+    if (warp + 4 * i < q_rows) regs[i].load_angles(cos_row, sin_row, lane);
+  if (warp == k_warp) k_regs.load_angles(cos_row, sin_row, lane);
+
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
   const int n_blocks = j_last - j_first + 1;
@@ -509,58 +553,29 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   };
   if (j_lo <= j_hi) issue(j_lo, 0);  // the cache pages travel while the new token is prepared
 
-  // The new token: queries of this tile's heads (rows beyond G are zero) and, in the block
-  // whose keys include it, its key and value. Warp w takes rows w, w + 4, ...; the key row
-  // goes to the warp after the last query row. Every row's loads are issued before any
-  // arithmetic, so the warps pay one memory latency, not one per row.
-  const bf16* row = qkv + (size_t)seq * q_stride;
-  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
-  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
-  const int q_rows = min(16, G - rt * 16);
-  const int k_warp = q_rows % 4;  // the warp with the fewest query rows
-  {
-    constexpr int MAX_ROWS = 4;  // 16 rows over 4 warps
-    HeadRow regs[MAX_ROWS];
-    HeadRow k_regs;
-    float v_regs[(D + 31) / 32];
 #pragma unroll
-    for (int i = 0; i < MAX_ROWS; ++i) {
-      const int r = warp + 4 * i;
-      if (r < q_rows) regs[i].load(row + (size_t)(kh * G + rt * 16 + r) * D, q_gain, gain_f32, cos_row, sin_row, lane);
+  for (int i = 0; i < MAX_ROWS; ++i) {
+    const int r = warp + 4 * i;
+    if (r < q_rows) {
+      regs[i].finish(q_s + r * DP, q_gain != nullptr, cos_t != nullptr, eps, lane);
+    } else if (r < 16) {
+      for (int d = lane; d < D; d += 32) q_s[r * DP + d] = __float2bfloat16_rn(0.f);
     }
-    const bool do_k = owns_new && warp == k_warp;
-    if (do_k) {
-      k_regs.load(row + (size_t)(HQ + kh) * D, k_gain, gain_f32, cos_row, sin_row, lane);
+  }
+  if (owns_new && warp == k_warp) {
+    k_regs.finish(kv_new, k_gain != nullptr, cos_t != nullptr, eps, lane);
 #pragma unroll
-      for (int i = 0; i < (D + 31) / 32; ++i) {
-        const int d = lane + 32 * i;
-        v_regs[i] = d < D ? __bfloat162float(row[(size_t)(HQ + HKV + kh) * D + d]) : 0.f;
-      }
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) kv_new[D + d] = __float2bfloat16_rn(v_regs[i]);
     }
-#pragma unroll
-    for (int i = 0; i < MAX_ROWS; ++i) {
-      const int r = warp + 4 * i;
-      if (r < q_rows) {
-        regs[i].finish(q_s + r * DP, q_gain != nullptr, cos_t != nullptr, eps, lane);
-      } else if (r < 16) {
-        for (int d = lane; d < D; d += 32) q_s[r * DP + d] = __float2bfloat16_rn(0.f);
-      }
-    }
-    if (do_k) {
-      k_regs.finish(kv_new, k_gain != nullptr, cos_t != nullptr, eps, lane);
-#pragma unroll
-      for (int i = 0; i < (D + 31) / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < D) kv_new[D + d] = __float2bfloat16_rn(v_regs[i]);
-      }
-      __syncwarp();
-      if (rt == 0) {
-        const int page = table[(size_t)slot * width + j_last % width];
-        const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
-        for (int d = lane; d < D; d += 32) {
-          k_cache[at + d] = kv_new[d];
-          v_cache[at + d] = kv_new[D + d];
-        }
+    __syncwarp();
+    if (rt == 0) {
+      const int page = table[(size_t)slot * width + j_last % width];
+      const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
+      for (int d = lane; d < D; d += 32) {
+        k_cache[at + d] = kv_new[d];
+        v_cache[at + d] = kv_new[D + d];
       }
     }
   }
