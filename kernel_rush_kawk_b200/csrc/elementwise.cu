@@ -91,10 +91,63 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, T* x_new, const T* x, const 
   }
 }
 
+// bfloat16 rows of up to 8192 elements (a multiple of 8): one 16-byte piece per thread, the
+// row stays in registers, global memory is read and written exactly once.
+__global__ void rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* x_new, const bf16* x, const bf16* __restrict__ branch,
+                                      const void* __restrict__ gain, int gain_f32, int H, float eps) {
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const size_t base = (size_t)blockIdx.x * H;
+  const int k = threadIdx.x * 8;
+  const bool on = k < H;
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = 0.f;
+  if (on) {
+    uint4 xv = *reinterpret_cast<const uint4*>(x + base + k);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    if (branch) {
+      uint4 bv = *reinterpret_cast<const uint4*>(branch + base + k);
+      const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
+      uint4 sv;
+      __nv_bfloat162* sp = reinterpret_cast<__nv_bfloat162*>(&sv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sp[j] = __floats2bfloat162_rn(__low2float(xp[j]) + __low2float(bp[j]), __high2float(xp[j]) + __high2float(bp[j]));
+        f[2 * j] = __low2float(sp[j]);
+        f[2 * j + 1] = __high2float(sp[j]);
+      }
+      *reinterpret_cast<uint4*>(x_new + base + k) = sv;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { f[2 * j] = __low2float(xp[j]); f[2 * j + 1] = __high2float(xp[j]); }
+    }
+  }
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sq += f[j] * f[j];
+  const float rstd = rsqrtf(block_sum(sq, scratch) / (float)H + eps);
+  if (on) {
+    uint4 ov;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      op[j] = __floats2bfloat162_rn(round_to<bf16>(f[2 * j] * rstd) * load_gain<bf16>(gain, k + 2 * j, gain_f32),
+                                    round_to<bf16>(f[2 * j + 1] * rstd) * load_gain<bf16>(gain, k + 2 * j + 1, gain_f32));
+    *reinterpret_cast<uint4*>(out + base + k) = ov;
+  }
+}
+
 template <typename T>
 int launch_rmsnorm(void* out, void* x_new, const void* x, const void* branch, const void* gain, int gain_f32, int rows,
                    int H, float eps, cudaStream_t stream) {
   if (rows == 0) return 0;
+  if (sizeof(T) == 2 && H % 8 == 0 && H <= 8192) {
+    const int threads = ((H / 8 + 31) / 32) * 32;
+    return (int)launch_pdl(rmsnorm_bf16x8_kernel, dim3(rows), dim3(threads), 0, stream, (bf16*)out, (bf16*)x_new,
+                           (const bf16*)x, (const bf16*)branch, gain, gain_f32, H, eps);
+  }
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 220 * 1024) return -2;  // a row must fit in shared memory
   int threads = H / 4 >= 1024 ? 1024 : (H / 4 >= 512 ? 512 : (H / 4 >= 256 ? 256 : 128));
@@ -141,6 +194,28 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
   out[r * I + i] = from_float<T>(s * u);
 }
 
+// bfloat16, I a multiple of 8: eight gate and eight up values per thread
+__global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, int I, long long n_pieces) {
+  const long long piece = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (piece >= n_pieces) return;
+  const int per_row = I / 8;
+  const long long r = piece / per_row;
+  const int i = (int)(piece % per_row) * 8;
+  const uint4 gv = *reinterpret_cast<const uint4*>(gu + r * 2 * I + i);
+  const uint4 uv = *reinterpret_cast<const uint4*>(gu + r * 2 * I + I + i);
+  const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  uint4 ov;
+  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float g0 = __low2float(gp[j]), g1 = __high2float(gp[j]);
+    const float s0 = round_to<bf16>(g0 / (1.0f + expf(-g0))), s1 = round_to<bf16>(g1 / (1.0f + expf(-g1)));
+    op[j] = __floats2bfloat162_rn(s0 * __low2float(up[j]), s1 * __high2float(up[j]));
+  }
+  *reinterpret_cast<uint4*>(out + r * I + i) = ov;
+}
+
 }  // namespace
 
 KRK_API int krk_rmsnorm(void* out, void* x_new, const void* x, const void* branch, const void* gain, int gain_f32,
@@ -161,6 +236,14 @@ KRK_API int krk_gather_rows(void* out, const void* table, const int* ids, int ro
 
 KRK_API int krk_swiglu(void* out, const void* gu, int rows, int I, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
+  if (dtype == KRK_DTYPE_BF16 && I % 8 == 0) {
+    const long long pieces = (long long)rows * (I / 8);
+    const long long blocks = (pieces + 255) / 256;
+    if (blocks > 0x7fffffffLL) return -3;
+    swiglu_bf16x8_kernel<<<(unsigned)blocks, 256, 0, stream>>>((bf16*)out, (const bf16*)gu, I, pieces);
+    KRK_CHECK_LAUNCH();
+    return 0;
+  }
   if ((I + 255) / 256 > 65535) return -3;
   dim3 grid(rows, (I + 255) / 256);
   if (dtype == KRK_DTYPE_F32)

@@ -78,6 +78,86 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const void* __res
   }
 }
 
+// bfloat16 and a head size of 16, 32, 64, 128 or 256: D/8 lanes share a head, 16 bytes each,
+// so a warp handles 32 / (D/8) heads with vector loads and stores. The partner of element i
+// (i < D/2) is element i + D/2, which sits D/16 lanes further; a shuffle brings it over.
+__global__ void qk_norm_rope_write_vec_kernel(bf16* __restrict__ qkv, const void* __restrict__ q_gain,
+                                              const void* __restrict__ k_gain, int gain_f32,
+                                              const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t,
+                                              const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                              const int* __restrict__ seq_slot, const int* __restrict__ table, int width,
+                                              bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int rows, int HQ,
+                                              int HKV, int D, float eps, int n_pos, int* error) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lph = D / 8;  // lanes per head
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % lph;  // this lane's 8 elements are [8 * sub, 8 * sub + 8)
+  const int heads = HQ + 2 * HKV;
+  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lph) + lane / lph;
+  const bool live = item < (long long)rows * heads;
+  const int row = live ? (int)(item / heads) : 0;
+  const int head = live ? (int)(item % heads) : 0;
+  const int raw_pos = row_pos[row];
+  const bool bad = raw_pos < 0 || raw_pos >= n_pos;  // flagged below; nothing is stored for such a row
+  const int pos = bad ? 0 : raw_pos;
+  const int half = D / 2;
+  bf16* src = qkv + (size_t)row * heads * D + (size_t)head * D + 8 * sub;
+  bf16* dst = src;
+  if (head >= HQ) {
+    const int kh = (head - HQ) % HKV;
+    const int page = page_of(table, width, seq_slot[row_seq[row]], pos);
+    bf16* cache = head < HQ + HKV ? k_cache : v_cache;
+    dst = cache + (((size_t)page * HKV + kh) * KRK_PAGE + (pos % KRK_PAGE)) * D + 8 * sub;
+  }
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (live) raw = *reinterpret_cast<const uint4*>(src);
+  const bool is_v = head >= HQ + HKV;
+  const void* gain = head < HQ ? q_gain : k_gain;
+  if (bad && live && error) atomicExch(error, 2);
+  float y[8];
+  const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    y[2 * j] = __low2float(rp[j]);
+    y[2 * j + 1] = __high2float(rp[j]);
+    sq += y[2 * j] * y[2 * j] + y[2 * j + 1] * y[2 * j + 1];
+  }
+  for (int o = lph >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // over the head's lanes
+  if (gain && !is_v) {
+    const float r = rsqrtf(sq / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = round_to<bf16>(load_gain<bf16>(gain, 8 * sub + j, gain_f32) * round_to<bf16>(y[j] * r));
+  }
+  float other[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) other[j] = __shfl_xor_sync(0xffffffffu, y[j], lph >> 1);
+  if (cos_t && !is_v) {
+    const bool first = 8 * sub < half;
+    const int i0 = first ? 8 * sub : 8 * sub - half;  // index into the half tables
+    const uint4 cv = *reinterpret_cast<const uint4*>(cos_t + (size_t)pos * half + i0);
+    const uint4 sv = *reinterpret_cast<const uint4*>(sin_t + (size_t)pos * half + i0);
+    const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&cv);
+    const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&sv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = (j & 1) ? __high2float(cp[j >> 1]) : __low2float(cp[j >> 1]);
+      const float s = (j & 1) ? __high2float(sp[j >> 1]) : __low2float(sp[j >> 1]);
+      // first half: y1*c - y2*s with y2 = other; second half: y2*c + y1*s with y1 = other
+      y[j] = first ? round_to<bf16>(y[j] * c) + round_to<bf16>(-other[j] * s)
+                   : round_to<bf16>(y[j] * c) + round_to<bf16>(other[j] * s);
+    }
+  }
+  if (live && !bad) {
+    uint4 ov;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+    *reinterpret_cast<uint4*>(dst) = is_v ? raw : ov;
+  }
+}
+
 }  // namespace
 
 // gains may be null (no q/k norm); cos/sin may be null (no rotation); the cache
@@ -89,6 +169,15 @@ KRK_API int krk_qk_norm_rope_write(void* qkv, const void* q_gain, const void* k_
   if (rows == 0) return 0;
   if (D % 2 || D > 4096) return -2;
   const long long items = (long long)rows * (HQ + 2 * HKV);
+  if (dtype == KRK_DTYPE_BF16 && (D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) {
+    const int per_warp = 32 / (D / 8);
+    const long long n_warps = (items + per_warp - 1) / per_warp;
+    const long long n_blocks = (n_warps + 7) / 8;
+    if (n_blocks > 0x7fffffffLL) return -3;
+    return (int)launch_pdl(qk_norm_rope_write_vec_kernel, dim3((unsigned)n_blocks), dim3(256), 0, stream, (bf16*)qkv,
+                           q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, row_seq, row_pos, seq_slot,
+                           table, width, (bf16*)k_cache, (bf16*)v_cache, rows, HQ, HKV, D, eps, n_pos, error);
+  }
   const int warps = 8;
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -3;
