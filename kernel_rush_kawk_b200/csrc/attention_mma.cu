@@ -100,6 +100,12 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], const bf16* q_
   }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One online-softmax update of a thread's two rows over NTILES*8 keys. s is in log2
 // units already (scaled by scale*log2(e)) and masked with -inf where invisible.
 template <int NTILES>
@@ -113,12 +119,12 @@ __device__ __forceinline__ void softmax_update(float (&s)[NTILES][4], float (&m)
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[h], mx);
     const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-    const float alpha = exp2f(m[h] - m_safe);
+    const float alpha = fast_exp2(m[h] - m_safe);
     float sum = 0.f;
 #pragma unroll
     for (int n = 0; n < NTILES; ++n) {
-      s[n][2 * h] = exp2f(s[n][2 * h] - m_safe);
-      s[n][2 * h + 1] = exp2f(s[n][2 * h + 1] - m_safe);
+      s[n][2 * h] = fast_exp2(s[n][2 * h] - m_safe);
+      s[n][2 * h + 1] = fast_exp2(s[n][2 * h + 1] - m_safe);
       sum += s[n][2 * h] + s[n][2 * h + 1];
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -172,6 +178,13 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, i
   }
   uint32_t qf[KSTEPS][4];
   load_q(qf, qp[0], qp[1], lane);
+  // the least position and the greatest window start among the warp's rows (an invalid row sees nothing)
+  int warp_min_pos = min(pos[0], pos[1]), warp_max_lo = max(lo[0], lo[1]);
+#pragma unroll
+  for (int o2 = 16; o2 > 0; o2 >>= 1) {
+    warp_min_pos = min(warp_min_pos, __shfl_xor_sync(0xffffffffu, warp_min_pos, o2));
+    warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, o2));
+  }
 
   // key blocks the tile can see
   const int last_tok = min(q_len - 1, (tile * 64 + 63) / G);
@@ -211,14 +224,23 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, i
     float s[8][4];
     qk_tile<8>(s, qf, ks, 0, lane);
     const int key_base = j * KRK_PAGE;
+    // a block that every row of the warp sees whole needs no mask (most blocks of a long prompt)
+    const bool whole = key_base + KRK_PAGE - 1 <= warp_min_pos && key_base >= warp_max_lo;
+    if (whole) {
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+      for (int n = 0; n < 8; ++n)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int key = key_base + n * 8 + 2 * t4 + (c & 1);
-        const int h = c >> 1;
-        s[n][c] = (key <= pos[h] && key >= lo[h]) ? s[n][c] * scale_log2 : -INFINITY;
-      }
+        for (int c = 0; c < 4; ++c) s[n][c] *= scale_log2;
+    } else {
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int key = key_base + n * 8 + 2 * t4 + (c & 1);
+          const int h = c >> 1;
+          s[n][c] = (key <= pos[h] && key >= lo[h]) ? s[n][c] * scale_log2 : -INFINITY;
+        }
+    }
     softmax_update<8>(s, m, l, o);
     pv_tile<8>(o, s, vs, 0, lane);
     __syncthreads();  // the stage is free for the load after next

@@ -42,6 +42,7 @@ _SIGNATURES = {
                                c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
+    "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -121,7 +122,10 @@ class Kernels:
         if flag:
             self.error.zero_()
             raise KernelError({1: "a token id outside the embedding table reached the device",
-                               2: "a position outside the rotary table reached the device"}.get(flag, f"flag {flag}"))
+                               2: "a position outside the rotary table reached the device",
+                               3: "a tensor-core GEMM gave up waiting for a free shared-memory stage",
+                               4: "a tensor-core GEMM gave up waiting for a TMA load",
+                               5: "a tensor-core GEMM gave up waiting for its accumulator"}.get(flag, f"flag {flag}"))
 
     def empty_like(self, x):
         return torch.empty_like(x)
@@ -172,6 +176,17 @@ class Kernels:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         self._ok(self.core.krk_gemm_nt(out.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
                                        _code(x.dtype), _code(out_dtype), self._stream()), "gemm")
+        return out
+
+    def gemm_tcgen05(self, x, w, swiglu_rows=0):
+        """y = x W^T (bfloat16) on the tcgen05 tensor cores; with ``swiglu_rows`` = I, W is
+        [2I, K] and y is the activated [M, I] product."""
+        M, K = x.shape
+        N = swiglu_rows if swiglu_rows else w.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        self._ok(self.core.krk_gemm_tcgen05(out.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0),
+                                            N, int(swiglu_rows > 0), self.error.data_ptr(), self._stream()),
+                 "tcgen05 gemm")
         return out
 
     def _skinny(self, x, w, out_dtype, swiglu_rows=0):

@@ -92,6 +92,27 @@ def test_linear(ops, dtype, mnk):
     close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), dtype, f"linear {mnk}, float32 out")
 
 
+@pytest.mark.parametrize("mnk", [(128, 128, 64), (128, 128, 512), (256, 384, 2560), (130, 200, 72), (77, 3000, 1000),
+                                 (2048, 2560, 4096)])
+def test_tcgen05_gemm(ops, mnk):
+    m, n, k = mnk
+    dtype = torch.bfloat16
+    x, w = rand((m, k), dtype, 80), rand((n, k), dtype, 81, 0.05)
+    ref = TorchOps(dtype)
+    close(ops.gemm_tcgen05(x, w), ref.linear(x, w), dtype, f"tcgen05 gemm {mnk}")
+    ops.check()
+
+
+@pytest.mark.parametrize("mik", [(128, 128, 128), (300, 272, 160), (2048, 9728, 2560)])
+def test_tcgen05_gemm_with_swiglu_epilogue(ops, mik):
+    m, inter, k = mik
+    dtype = torch.bfloat16
+    x, w = rand((m, k), dtype, 82), rand((2 * inter, k), dtype, 83, 0.05)
+    ref = TorchOps(dtype)
+    close(ops.gemm_tcgen05(x, w, swiglu_rows=inter), ref.gate_up_swiglu(x, w, inter), dtype, f"tcgen05 gate/up {mik}")
+    ops.check()
+
+
 @pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
 @pytest.mark.parametrize("nk", [(96, 64), (160, 2560), (301, 96), (2560, 9728)])
 def test_fused_norm_linear_bfloat16(ops, rows, nk):
