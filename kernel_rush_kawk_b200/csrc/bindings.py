@@ -42,7 +42,7 @@ _SIGNATURES = {
                                c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
-    "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -52,6 +52,8 @@ _ATTN_SIGNATURES = {
                               c_int, _P],
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
+    "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
+                                      c_float, c_int, _P, _P],
     "krk_attention_decode_fused": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
                                    _P, c_int, c_float, c_int, c_int, c_int, _P, _P],
 }
@@ -94,6 +96,7 @@ class Kernels:
         self.has_skinny = hasattr(self.core, "krk_skinny_linear")
         self._partials: dict = {}
         self._select_scratch = None
+        self.use_tcgen05_attention = True
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -125,7 +128,9 @@ class Kernels:
                                2: "a position outside the rotary table reached the device",
                                3: "a tensor-core GEMM gave up waiting for a free shared-memory stage",
                                4: "a tensor-core GEMM gave up waiting for a TMA load",
-                               5: "a tensor-core GEMM gave up waiting for its accumulator"}.get(flag, f"flag {flag}"))
+                               5: "a tensor-core GEMM gave up waiting for its accumulator"}.get(
+                                   flag, f"a tensor-core attention kernel gave up on a barrier wait (code {flag})"
+                                   if 6 <= flag <= 10 else f"flag {flag}"))
 
     def empty_like(self, x):
         return torch.empty_like(x)
@@ -178,14 +183,14 @@ class Kernels:
                                        _code(x.dtype), _code(out_dtype), self._stream()), "gemm")
         return out
 
-    def gemm_tcgen05(self, x, w, swiglu_rows=0):
+    def gemm_tcgen05(self, x, w, swiglu_rows=0, variant=0):
         """y = x W^T (bfloat16) on the tcgen05 tensor cores; with ``swiglu_rows`` = I, W is
         [2I, K] and y is the activated [M, I] product."""
         M, K = x.shape
         N = swiglu_rows if swiglu_rows else w.shape[0]
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         self._ok(self.core.krk_gemm_tcgen05(out.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0),
-                                            N, int(swiglu_rows > 0), self.error.data_ptr(), self._stream()),
+                                            N, int(swiglu_rows > 0), variant, self.error.data_ptr(), self._stream()),
                  "tcgen05 gemm")
         return out
 
@@ -299,6 +304,14 @@ class Kernels:
                 batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(),
                 cache.v.data_ptr(), batch.n_seqs, scale, win, splits, parts.data_ptr(), self._stream()),
                 "decode attention")
+        elif (fast and self.use_tcgen05_attention and head_dim in (64, 128) and hasattr(lib, "krk_attention_prefill_tcgen05")
+              and batch.max_q_len * (heads // cache.kv_heads) >= 128 and stride % 8 == 0):
+            # long steps: the tcgen05 kernel (128-row tiles of (token, group member) pairs)
+            self._ok(lib.krk_attention_prefill_tcgen05(
+                out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),
+                batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(), batch.cu_q.data_ptr(), cache.table.data_ptr(),
+                cache.width, cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], batch.n_seqs, batch.max_q_len,
+                scale, win, self.error.data_ptr(), self._stream()), "tcgen05 prefill attention")
         elif fast and hasattr(lib, "krk_attention_prefill"):
             self._ok(lib.krk_attention_prefill(
                 out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),

@@ -15,99 +15,26 @@
 // to). One 128x128 output tile per block (two accumulators with SwiGLU). A ring of
 // shared-memory stages connects the roles through mbarriers. Every wait is bounded: a wait
 // that runs out sets the error word and the block leaves, after freeing its tensor memory.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;      // tile; BK * 2 bytes = one 128-byte swizzle row
+using namespace tc;
+
+constexpr int BM = 128, BK = 64;                // tile rows and depth; BK * 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr long long SPIN_LIMIT = 1LL << 24;     // polls of a barrier before a wait gives up
+constexpr uint32_t A_BYTES = BM * BK * 2;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait on a phase parity; false if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (long long i = 0; i < SPIN_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
-// start address, stride between 8-row groups = 1024 bytes, descriptor version 1, swizzle mode 2.
-__device__ __forceinline__ uint64_t umma_desc(const void* smem_tile) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_u32(smem_tile) & 0x3FFFF) >> 4);  // bits 0..13: address / 16
-  d |= (uint64_t)1 << 16;                                  // bits 16..29: leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;                        // bits 32..45: stride byte offset / 16
-  d |= (uint64_t)1 << 46;                                  // bits 46..47: descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                                  // bits 61..63: 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptor: bfloat16 A and B, both K-major, float32 accumulator, M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-template <bool SWIGLU, int STAGES>
-__global__ void __launch_bounds__(THREADS, 1)
+template <bool SWIGLU, int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ C, int M, int N, int K, int ldc, int up_row_offset, int* __restrict__ error) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int NB = SWIGLU ? 2 : 1;                       // weight tiles per stage
+  constexpr uint32_t B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + NB * B_BYTES;
-  constexpr uint32_t TMEM_COLS = SWIGLU ? 256 : 128;
+  constexpr uint32_t TMEM_COLS = NB * BN;                  // 128, 256 or 512: a power of two
   // 1024-byte alignment of every tile: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * STAGE_BYTES);
@@ -144,12 +71,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(full_bar + s, STAGE_BYTES);
       tma_load_2d(stage, &map_a, full_bar + s, kb * BK, m0);
-      tma_load_2d(stage + A_BYTES, &map_w, full_bar + s, kb * BK, n0);
-      if (SWIGLU) tma_load_2d(stage + A_BYTES + B_BYTES, &map_w, full_bar + s, kb * BK, up_row_offset + n0);
+#pragma unroll
+      for (int h = 0; h < BN / 128; ++h) {  // the weight box has 128 rows
+        tma_load_2d(stage + A_BYTES + h * (128 * BK * 2), &map_w, full_bar + s, kb * BK, n0 + 128 * h);
+        if (SWIGLU)
+          tma_load_2d(stage + A_BYTES + B_BYTES + h * (128 * BK * 2), &map_w, full_bar + s, kb * BK,
+                      up_row_offset + n0 + 128 * h);
+      }
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
-    constexpr uint32_t idesc = umma_idesc(BM, BN);
+    constexpr uint32_t idesc = umma_idesc(BM, BN);  // N up to 256 in one instruction
     bool ok = true;
     for (int kb = 0; kb < k_blocks && ok; ++kb) {
       const int s = kb % STAGES;
@@ -186,20 +118,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < M) {
           bf16* dst = C + (size_t)row * ldc + n0 + c0;
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float v0 = __uint_as_float(g[j]), v1 = __uint_as_float(g[j + 1]);
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(g[j]);
             if (SWIGLU) {
-              const float g0 = round_to<bf16>(v0), g1 = round_to<bf16>(v1);
-              v0 = round_to<bf16>(g0 / (1.0f + expf(-g0))) * round_to<bf16>(__uint_as_float(u[j]));
-              v1 = round_to<bf16>(g1 / (1.0f + expf(-g1))) * round_to<bf16>(__uint_as_float(u[j + 1]));
+              const float gj = round_to<bf16>(v[j]);
+              v[j] = round_to<bf16>(gj / (1.0f + __expf(-gj))) * round_to<bf16>(__uint_as_float(u[j]));
             }
-            const int col = n0 + c0 + j;
-            if (col + 1 < N) {
-              *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(v0, v1);
-            } else if (col < N) {
-              dst[j] = __float2bfloat16_rn(v0);
+          }
+          if (n0 + c0 + 32 <= N && (ldc % 8) == 0 && ((uintptr_t)C & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {  // 16-byte stores
+              uint4 pk;
+              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) pp[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+              *reinterpret_cast<uint4*>(dst + j) = pk;
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < N) dst[j] = __float2bfloat16_rn(v[j]);
           }
         }
       }
@@ -213,48 +153,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-  static EncodeTiled fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiled)p;
-  }
-  return fn;
-}
-
-// A row-major [rows, cols] bfloat16 matrix with row stride ld elements, read in boxes of 128 rows x 64 columns.
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld) {
-  EncodeTiled fn = encode_fn();
-  if (!fn) return -6;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -7;
-}
-
-template <bool SWIGLU>
+template <bool SWIGLU, int BN, int STAGES>
 int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc, int* error,
            cudaStream_t stream) {
-  constexpr int STAGES = SWIGLU ? 4 : 6;
   constexpr int NB = SWIGLU ? 2 : 1;
-  constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + NB * B_BYTES) + 1024 + (2 * STAGES + 1) * 8 + 16;
+  constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + NB * BN * BK * 2) + 1024 + (2 * STAGES + 1) * 8 + 16;
   CUtensorMap map_a, map_w;
-  int rc = make_map(&map_a, A, M, K, lda);
+  int rc = make_map_bf16(&map_a, A, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&map_w, W, SWIGLU ? 2 * N : N, K, ldw);
+  rc = make_map_bf16(&map_w, W, SWIGLU ? 2 * N : N, K, ldw, 128);
   if (rc) return rc;
-  auto kern = gemm_tcgen05_kernel<SWIGLU, STAGES>;
+  auto kern = gemm_tcgen05_kernel<SWIGLU, BN, STAGES>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
@@ -274,10 +183,13 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, 
 // ldw multiples of 8 and 16-byte aligned base addresses (the TMA's rules). error: device word that a
 // barrier wait which ran out sets to 3, 4 or 5.
 KRK_API int krk_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                             int swiglu, int* error, cudaStream_t stream) {
+                             int swiglu, int variant, int* error, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || (ldc & 1) || ((uintptr_t)C & 3))
     return -2;
-  return swiglu ? launch<true>(C, A, W, M, N, K, lda, ldw, ldc, error, stream)
-                : launch<false>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  // variant: 0 = 128x256 tile, one block per SM (with swiglu: 128x128 gate + 128x128 up);
+  //          1 = 128x128 tile, three stages, two blocks per SM
+  if (swiglu) return launch<true, 128, 4>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  if (variant == 1) return launch<false, 128, 3>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  return launch<false, 256, 4>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
 }

@@ -264,6 +264,39 @@ def test_fused_decode_attention_against_the_two_kernel_path(ops, shape, window, 
     close(got, want, dtype, f"fused decode attention {shape} window {window} seqs {n_seqs}")
 
 
+@pytest.mark.parametrize("shape", [(8, 2, 64), (32, 8, 128), (6, 2, 128), (5, 1, 64)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_tcgen05_prefill_attention(ops, shape, window):
+    """Long steps in bfloat16 at head sizes 64 and 128 take the tcgen05 kernel: prompts of
+    unequal lengths from position 0, then pieces that continue them, against the plain
+    reference; with the mma.sync kernel of the same library as a second opinion."""
+    heads, kv_heads, D = shape
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    width, n_slots = 10, 3
+    cache = make_cache(34, kv_heads, D, n_slots, width, dtype, 90)
+    cache.window = window
+    scale = 1.0 / math.sqrt(D)
+    row_w = (heads + 2 * kv_heads) * D
+    steps = [([1, 2, 0], [0, 0, 0], [300, 129, 64]), ([2, 1], [129, 300], [200, 131])]
+    for s, (slots, starts, q_lens) in enumerate(steps):
+        batch = make_batch(slots, starts, q_lens)
+        qkv = rand((batch.n_rows, row_w), dtype, 91 + s, 1.0)
+        # the step's own keys and values go into the cache first, as in the engine
+        ops.qk_norm_rope_write(qkv, heads, kv_heads, D, None, None, 1e-6, None, None, batch, cache)
+        assert ops.use_tcgen05_attention
+        got = ops.attention(qkv, heads, kv_heads, D, batch, cache, scale, window)
+        ops.check()
+        want = ref.attention(qkv, heads, kv_heads, D, batch, cache, scale, window)
+        close(got, want, dtype, f"tcgen05 attention step {s} {shape} window {window}")
+        ops.use_tcgen05_attention = False
+        try:
+            other = ops.attention(qkv, heads, kv_heads, D, batch, cache, scale, window)
+        finally:
+            ops.use_tcgen05_attention = True
+        close(got, other, dtype, "tcgen05 against mma.sync")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_len", [1, 37])
 def test_one_far_key_among_hundreds_decides(ops, dtype, q_len):
