@@ -171,7 +171,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       const int key0 = jb * KEYS;
       if (!mbar_wait(s_full, it & 1)) { if (lane == 0) atomicExch(error, 9); ok = false; break; }
       tc_fence_after();
-      const bool whole = key0 + KEYS - 1 <= pos && key0 >= lo;
+      const bool whole = key0 + KEYS - 1 <= pos && key0 >= lo;  // the row sees every key of the block
       // pass 1: the row's maximum
       float mx = -INFINITY;
 #pragma unroll
@@ -179,11 +179,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         uint32_t s[32];
         tmem_ld_32x32(tmem_s + lane_addr + c0, s);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (whole) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = key0 + c0 + j;
-          const float v = __uint_as_float(s[j]);
-          if (whole || (key <= pos && key >= lo)) mx = fmaxf(mx, v);
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(s[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c0 + j;
+            if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(s[j]));
+          }
         }
       }
       const float m_new = fmaxf(m, mx * scale_log2);
@@ -197,13 +201,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         tmem_ld_32x32(tmem_s + lane_addr + c0, s);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         float p[32];
+        if (whole) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = key0 + c0 + j;
-          const bool see = whole || (key <= pos && key >= lo);
-          p[j] = see ? fast_exp2(__uint_as_float(s[j]) * scale_log2 - m_safe) : 0.f;
-          sum += p[j];
+          for (int j = 0; j < 32; ++j) p[j] = fast_exp2(fmaf(__uint_as_float(s[j]), scale_log2, -m_safe));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c0 + j;
+            p[j] = (key <= pos && key >= lo) ? fast_exp2(fmaf(__uint_as_float(s[j]), scale_log2, -m_safe)) : 0.f;
+          }
         }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum += p[j];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {  // four 16-byte pieces of 8 keys
           uint4 pk;
