@@ -42,7 +42,7 @@ _SIGNATURES = {
                                c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
-    "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -183,14 +183,16 @@ class Kernels:
                                        _code(x.dtype), _code(out_dtype), self._stream()), "gemm")
         return out
 
-    def gemm_tcgen05(self, x, w, swiglu_rows=0, variant=0):
-        """y = x W^T (bfloat16) on the tcgen05 tensor cores; with ``swiglu_rows`` = I, W is
-        [2I, K] and y is the activated [M, I] product."""
+    def gemm_tcgen05(self, x, w, swiglu_rows=0, variant=0, out_float32=False):
+        """y = x W^T (bfloat16 inputs) on the tcgen05 tensor cores; with ``swiglu_rows`` = I,
+        W is [2I, K] and y is the activated [M, I] product; ``out_float32`` keeps the
+        accumulator's precision (output-head logits)."""
         M, K = x.shape
         N = swiglu_rows if swiglu_rows else w.shape[0]
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
         self._ok(self.core.krk_gemm_tcgen05(out.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0),
-                                            N, int(swiglu_rows > 0), variant, self.error.data_ptr(), self._stream()),
+                                            N, int(swiglu_rows > 0), variant, int(out_float32), self.error.data_ptr(),
+                                            self._stream()),
                  "tcgen05 gemm")
         return out
 
@@ -244,7 +246,12 @@ class Kernels:
         x = self._resolve(x)
         if x.shape[0] == 0:
             return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
-        if w.dtype == torch.float32 or out_float32:
+        if w.dtype == torch.float32:
+            return self._gemm_nt(x, w, out_dtype)
+        if out_float32:  # many rows of float32 logits: the tcgen05 GEMM keeps the accumulator's precision
+            if (x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+                    and w.data_ptr() % 16 == 0 and hasattr(self.core, "krk_gemm_tcgen05")):
+                return self.gemm_tcgen05(x, w, out_float32=True)
             return self._gemm_nt(x, w, out_dtype)
         return torch.matmul(x, w.t())
 
@@ -274,8 +281,11 @@ class Kernels:
             n = batch.n_seqs
             out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
             row_tiles = -(-(heads // cache.kv_heads) // 16)
-            want = -(-296 // (n * cache.kv_heads * row_tiles))
-            splits = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
+            # key splits (blocks per cluster) by the number of (sequence, kv head, row tile) items alone,
+            # never by lengths, so a captured step stays valid; measured best on B200 at 1, 8 and 64
+            # sequences of the 4B shape: 8, 4 and 2
+            items = n * cache.kv_heads * row_tiles
+            splits = 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 600 else 1
             gain = q_gain if q_gain is not None else k_gain
             n_pos = cos.shape[0] if cos is not None else 0x7fffffff
             self._ok(lib.krk_attention_decode_fused(

@@ -26,10 +26,10 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr uint32_t A_BYTES = BM * BK * 2;
 
-template <bool SWIGLU, int BN, int STAGES>
+template <bool SWIGLU, int BN, int STAGES, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    bf16* __restrict__ C, int M, int N, int K, int ldc, int up_row_offset, int* __restrict__ error) {
+                    TOut* __restrict__ C, int M, int N, int K, int ldc, int up_row_offset, int* __restrict__ error) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int NB = SWIGLU ? 2 : 1;                       // weight tiles per stage
   constexpr uint32_t B_BYTES = BN * BK * 2;
@@ -117,7 +117,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (SWIGLU) tmem_ld_32x32(taddr + BN, u);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < M) {
-          bf16* dst = C + (size_t)row * ldc + n0 + c0;
+          TOut* dst = C + (size_t)row * ldc + n0 + c0;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -127,19 +127,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               v[j] = round_to<bf16>(gj / (1.0f + __expf(-gj))) * round_to<bf16>(__uint_as_float(u[j]));
             }
           }
-          if (n0 + c0 + 32 <= N && (ldc % 8) == 0 && ((uintptr_t)C & 15) == 0) {
+          constexpr int PER16 = 16 / sizeof(TOut);  // elements per 16-byte store
+          if (n0 + c0 + 32 <= N && (ldc % PER16) == 0 && ((uintptr_t)C & 15) == 0) {
+            if (sizeof(TOut) == 4) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {  // 16-byte stores
-              uint4 pk;
-              __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) pp[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
-              *reinterpret_cast<uint4*>(dst + j) = pk;
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) pp[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = pk;
+              }
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + c0 + j < N) dst[j] = __float2bfloat16_rn(v[j]);
+              if (n0 + c0 + j < N) dst[j] = from_float<TOut>(v[j]);
           }
         }
       }
@@ -153,7 +160,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-template <bool SWIGLU, int BN, int STAGES>
+template <bool SWIGLU, int BN, int STAGES, typename TOut>
 int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc, int* error,
            cudaStream_t stream) {
   constexpr int NB = SWIGLU ? 2 : 1;
@@ -163,7 +170,7 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, 
   if (rc) return rc;
   rc = make_map_bf16(&map_w, W, SWIGLU ? 2 * N : N, K, ldw, 128);
   if (rc) return rc;
-  auto kern = gemm_tcgen05_kernel<SWIGLU, BN, STAGES>;
+  auto kern = gemm_tcgen05_kernel<SWIGLU, BN, STAGES, TOut>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
@@ -171,7 +178,7 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, 
     configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kern<<<grid, THREADS, SMEM, stream>>>(map_a, map_w, (bf16*)C, M, N, K, ldc, N, error);
+  kern<<<grid, THREADS, SMEM, stream>>>(map_a, map_w, (TOut*)C, M, N, K, ldc, N, error);
   KRK_CHECK_LAUNCH();
   return 0;
 }
@@ -183,13 +190,17 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, 
 // ldw multiples of 8 and 16-byte aligned base addresses (the TMA's rules). error: device word that a
 // barrier wait which ran out sets to 3, 4 or 5.
 KRK_API int krk_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
-                             int swiglu, int variant, int* error, cudaStream_t stream) {
+                             int swiglu, int variant, int out_f32, int* error, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || (ldc & 1) || ((uintptr_t)C & 3))
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)C & 3))
     return -2;
   // variant: 0 = 128x256 tile, one block per SM (with swiglu: 128x128 gate + 128x128 up);
   //          1 = 128x128 tile, three stages, two blocks per SM
-  if (swiglu) return launch<true, 128, 4>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
-  if (variant == 1) return launch<false, 128, 3>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
-  return launch<false, 256, 4>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  if (out_f32) {  // float32 output (output-head logits); no activation
+    if (swiglu) return -4;
+    return launch<false, 256, 4, float>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  }
+  if (swiglu) return launch<true, 128, 4, bf16>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  if (variant == 1) return launch<false, 128, 3, bf16>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+  return launch<false, 256, 4, bf16>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
 }

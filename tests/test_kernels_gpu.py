@@ -100,6 +100,7 @@ def test_tcgen05_gemm(ops, mnk):
     x, w = rand((m, k), dtype, 80), rand((n, k), dtype, 81, 0.05)
     ref = TorchOps(dtype)
     close(ops.gemm_tcgen05(x, w), ref.linear(x, w), dtype, f"tcgen05 gemm {mnk}")
+    close(ops.gemm_tcgen05(x, w, out_float32=True), ref.linear(x, w, out_float32=True), dtype, f"tcgen05 gemm {mnk}, float32 out")
     ops.check()
 
 
