@@ -1,0 +1,68 @@
+"""The Qwen3-4B layer sizes (hidden 2560, 32 query / 8 kv heads of 128, intermediate 9728,
+vocabulary 151,936, tied head, theta 5e6) with two layers and random weights: the sizes at
+which the serving kernels really run (tcgen05 attention and logits GEMM, 4- and 8-warp decode
+GEMVs, cluster-merged decode attention), against the plain implementation, in 32-bit and in
+bfloat16, whole and token by token, alone and in an unequal batch."""
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def big_folder(tmp_path_factory):
+    from kernel_rush_kawk_b200 import Qwen3Config, write_model_folder
+
+    base = Qwen3Config.preset("qwen3_4b").to_dict()
+    cfg = Qwen3Config.from_dict({**base, "num_hidden_layers": 2})
+    scale = {f"model.layers.{i}.self_attn.{n}_norm.weight": 1.5 for i in range(2) for n in ("q", "k")}
+    return write_model_folder(tmp_path_factory.mktemp("big") / "m", cfg, 77, std=0.02, gain_std=0.05, scale=scale)
+
+
+@pytest.fixture(scope="module")
+def sequences(big_folder):
+    g = torch.Generator().manual_seed(5)
+    return [torch.randint(0, 151936, (n,), generator=g).tolist() for n in (150, 40, 9)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_four_b_layer_sizes_against_plain(big_folder, sequences, dtype):
+    from kernel_rush_kawk_b200 import Engine, StepEntry
+
+    cfg, w = plain.read_folder(big_folder)
+    rounding = None if dtype == "float32" else torch.bfloat16
+    wide = torch.float64 if dtype == "float32" else torch.float32
+    refs = [plain.forward_logits(cfg, w, s, wide, rounding).float() for s in sequences]
+    engine = Engine(big_folder, dtype=dtype, max_tokens=1024, max_slots=4)
+    cache = engine.cache
+    # (1) the longest request whole: 150 tokens x 4 group members = tiles of the tcgen05 kernel in bfloat16
+    slot = cache.alloc()
+    out = engine.step([StepEntry(slot, sequences[0], list(range(len(sequences[0]))))])
+    cache.free(slot)
+    assert_close(out, refs[0], dtype, f"4B sizes, whole, {dtype}")
+    # (2) an unequal batch: prompts, then one token each until every sequence is used up
+    cuts = [130, 20, 1]
+    slots = [cache.alloc() for _ in sequences]
+    got = [[] for _ in sequences]
+    out = engine.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, sequences, cuts)])
+    row = 0
+    for i, c in enumerate(cuts):
+        got[i].append(out[row:row + c].float().cpu())
+        row += c
+    fed = list(cuts)
+    while any(f < len(s) for f, s in zip(fed, sequences)):
+        live = [i for i in range(3) if fed[i] < len(sequences[i])]
+        out = engine.step([StepEntry(slots[i], [sequences[i][fed[i]]], [0]) for i in live]).float().cpu()
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1])
+            fed[i] += 1
+    for i, ref in enumerate(refs):
+        assert_close(torch.cat(got[i]), ref, dtype, f"4B sizes, batch, request {i}, {dtype}")
+    for s in slots:
+        cache.free(s)
+    cache.check()
+    engine.ops.check()
