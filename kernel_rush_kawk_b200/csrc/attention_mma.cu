@@ -411,9 +411,10 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, const float* __re
 }
 
 
+constexpr int FSTAGES = 2;  // page stages of the fused single-token kernel; three were measured: slower at batch 8 (fewer blocks fit an SM), no faster at 64
 constexpr size_t FUSED_BASE_BYTES =
-    ((size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)4 * 16 * (D + 2) * sizeof(float))
-        ? (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)4 * 16 * (D + 2) * sizeof(float);
+    ((size_t)FSTAGES * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)4 * 16 * (D + 2) * sizeof(float))
+        ? (size_t)FSTAGES * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t PAGE_SMEM = (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16);
 constexpr size_t RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t DECODE_SMEM = PAGE_SMEM > RED_SMEM ? PAGE_SMEM : RED_SMEM;
@@ -566,14 +567,17 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
 
   const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
   const size_t head_off = (size_t)kh * KRK_PAGE * D;
-  auto issue = [&](int j, int stage) {
-    const int page = table[(size_t)slot * width + j % width];
-    bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
-    load_page(ks, k_cache + (size_t)page * page_stride + head_off);
-    load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+  auto issue = [&](int j) {  // page j of this block's range into stage (j - j_lo) % FSTAGES; one group per call
+    if (j <= j_hi) {
+      const int page = table[(size_t)slot * width + j % width];
+      bf16* ks = smem + (size_t)((j - j_lo) % FSTAGES) * 2 * TILE_ELEMS;
+      load_page(ks, k_cache + (size_t)page * page_stride + head_off);
+      load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+    }
     cp_async_commit();
   };
-  if (j_lo <= j_hi) issue(j_lo, 0);  // the cache pages travel while the new token is prepared
+#pragma unroll
+  for (int i = 0; i < FSTAGES - 1; ++i) issue(j_lo + i);  // the cache pages travel while the new token is prepared
 
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i) {
@@ -618,13 +622,9 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
 
   for (int j = j_lo; j <= j_hi; ++j) {
-    const int stage = (j - j_lo) & 1;
-    if (j + 1 <= j_hi) {
-      issue(j + 1, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int stage = (j - j_lo) % FSTAGES;
+    issue(j + FSTAGES - 1);            // into the stage that the previous iteration finished with
+    cp_async_wait<FSTAGES - 1>();      // all but the newest FSTAGES - 1 groups: page j has landed
     __syncthreads();
     bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
     bf16* vs = ks + TILE_ELEMS;
@@ -650,6 +650,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     __syncthreads();
   }
 
+  cp_async_wait<0>();
   // Merge the four warps through shared memory, in warp order, and push the block's partial
   // (m, l, o[D]) per row straight into block 0's inbox through distributed shared memory.
   // One cluster barrier later block 0 holds every split's partial locally and merges them in
@@ -720,8 +721,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
 }
 
 constexpr size_t FUSED_RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
-constexpr size_t FUSED_BASE = PAGE_SMEM > FUSED_RED_SMEM ? PAGE_SMEM : FUSED_RED_SMEM;
-constexpr size_t FUSED_SMEM = FUSED_BASE + (size_t)(16 * DP + 2 * D) * sizeof(bf16);
+constexpr size_t FUSED_SMEM = FUSED_BASE_BYTES + (size_t)(16 * DP + 2 * D) * sizeof(bf16);
 
 }  // namespace
 
