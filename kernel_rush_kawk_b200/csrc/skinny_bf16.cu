@@ -24,7 +24,7 @@
 namespace {
 
 constexpr int CHUNK = 32;        // k values per fragment load
-constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 bytes each)
+constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 bytes each); DEEP doubles it
 
 // NT: 8-row batch tiles (1 or 2). RT: 16-row weight tiles per block; with SWIGLU the
 // block streams RT gate tiles and RT up tiles.
@@ -35,7 +35,7 @@ constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 
 // ring-full of copies is issued before anything else (before the wait on the
 // previous kernel, before the norm prologue), so the memory system is busy from the
 // block's first instruction.
-template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
+template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ W,
               const bf16* __restrict__ branch, const void* __restrict__ gain, int gain_f32, bf16* __restrict__ x_new,
@@ -44,7 +44,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   KRK_TRACE_DECL
   constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;  // 16-row weight tiles this block streams
-  constexpr int STAGES = RING_LOADS / TILES;
+  constexpr int STAGES = (DEEP ? 2 : 1) * RING_LOADS / TILES;
   constexpr int XSLOTS = NORM ? 0 : NT;          // without the prologue the batch rows ride in the ring too
   constexpr int SLOTS = TILES * 2 + XSLOTS;      // 16-byte pieces per thread and stage
   constexpr size_t RING_BYTES = (size_t)STAGES * SLOTS * THREADS * 16;
@@ -254,12 +254,12 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   KRK_TRACE_END(K)
 }
 
-template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
+template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false>
 int launch_warps(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
   constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;
-  constexpr int STAGES = RING_LOADS / TILES;
+  constexpr int STAGES = (DEEP ? 2 : 1) * RING_LOADS / TILES;
   int pitch = 0;
   constexpr int SLOTS = TILES * 2 + (NORM ? 0 : NT);
   size_t smem = (size_t)STAGES * SLOTS * THREADS * 16 + (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
@@ -269,7 +269,7 @@ int launch_warps(void* out, const void* x, const void* W, const void* branch, co
     smem += (size_t)M * pitch * 2;
   }
   if (smem > 220 * 1024) return -2;
-  auto kern = skinny_kernel<WARPS, NT, RT, SWIGLU, NORM, TOut>;
+  auto kern = skinny_kernel<WARPS, NT, RT, SWIGLU, NORM, TOut, DEEP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -290,6 +290,8 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
   if (blocks > 2 * 148 && blocks <= 5 * 148)
     return launch_warps<4, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  // (a ring twice as deep for kernels of about one block per SM was measured: slower, because the
+  // next kernel's blocks then no longer fit beside it to prefetch their weights)
   return launch_warps<8, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
 }
 
