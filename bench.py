@@ -254,7 +254,7 @@ def run_ours(args) -> dict:
 def main() -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=128)
+    p.add_argument("--steps", type=int, default=256)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b64"],
