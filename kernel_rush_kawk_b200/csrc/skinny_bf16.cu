@@ -106,6 +106,8 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   // per stage, empty or not, so that group counting stays simple.
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) issue_w(i);
+  // The next kernel's blocks may start at once: they prefetch their weights beside this kernel.
+  // (Letting them in only after this kernel's streaming was measured: slower.)
   grid_launch_dependents();
   grid_dependency_wait();  // x, branch come from earlier kernels; x_new may still be read by them
   KRK_TRACE_READY
