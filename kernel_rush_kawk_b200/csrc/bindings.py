@@ -82,7 +82,7 @@ class Kernels:
     SKINNY_MAX_ROWS = 16  # rows up to which the fused skinny kernels serve a bfloat16 product
     # Every block of a skinny product redoes the norm of all rows in its prologue. That is
     # cheaper than a separate norm kernel for one or two rows and dearer beyond.
-    FUSED_NORM_MAX_ROWS = int(__import__('os').environ.get('KRK_FUSED_ROWS', '2'))
+    FUSED_NORM_MAX_ROWS = 2
 
     def __init__(self, head_dims=(), device="cuda:0"):
         if not torch.cuda.is_available():

@@ -143,7 +143,7 @@ class Model:
         stream = Stream(x)
         for run, entry in enumerate(self.plan.schedule):
             stream = self.blocks[entry.layer].forward(ctx, stream, ctx.cache_view(run))
-        if want_rows is not None:
+        if want_rows is not None and not getattr(ctx.batch, "want_all", False):  # all rows in order: nothing to gather
             stream.x = ops.gather_rows(stream.x, want_rows)
             if stream.branch is not None:
                 stream.branch = ops.gather_rows(stream.branch, want_rows)

@@ -67,6 +67,7 @@ class BatchMeta:
         self.max_q_len = 1
         self.max_kv_len = 1
         self.is_decode = False
+        self.want_all = False  # the wanted rows are all rows, in order
         self.slots: list[int] = []
         self.starts: list[int] = []
         self.q_lens: list[int] = []
@@ -97,6 +98,7 @@ class BatchMeta:
         self.max_q_len = max(q_lens)
         self.max_kv_len = max(s + n for s, n in zip(starts, q_lens))
         self.is_decode = self.max_q_len == 1
+        self.want_all = list(want_rows) == list(range(self.n_rows))
         self.slots, self.starts, self.q_lens = list(slots), list(starts), q_lens
 
     @property
