@@ -73,8 +73,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   uint64_t* o_full = kv_full + 3;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_full + 4);
 
-  const int seq = blockIdx.z, kh = blockIdx.y;
-  const int tile = gridDim.x - 1 - blockIdx.x;  // long tiles first
+  // blockIdx.x counts (tile, kv head) pairs with the tile as the slow index, descending: blocks start in
+  // launch order, so the tiles with the most key blocks, of every kv head, run first and the short ones
+  // fill the tail
+  const int seq = blockIdx.y, kh = blockIdx.x % HKV;
+  const int tile = gridDim.x / HKV - 1 - blockIdx.x / HKV;
   const int G = HQ / HKV;
   const int q_len = seq_qlen[seq];
   const int n_rows = q_len * G;
@@ -275,7 +278,7 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
   if (n_seqs == 0 || max_q_len == 0) return 0;
   const int G = HQ / HKV;
   const long long tiles = ((long long)max_q_len * G + ROWS - 1) / ROWS;
-  if (tiles > 0x7fffffffLL || HKV > 65535 || n_seqs > 65535) return -3;
+  if (tiles * HKV > 0x7fffffffLL || n_seqs > 65535) return -3;
   if ((q_stride % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return -2;
   CUtensorMap map_k, map_v;
   const long long rows = (long long)n_pages * HKV * KRK_PAGE;
@@ -289,7 +292,7 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((unsigned)tiles, HKV, n_seqs);
+  dim3 grid((unsigned)(tiles * HKV), n_seqs, 1);
   attention_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
       map_k, map_v, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
       scale * LOG2E, window, error);
