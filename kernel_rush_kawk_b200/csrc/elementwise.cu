@@ -114,7 +114,7 @@ __global__ void rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* x_new, const
       __nv_bfloat162* sp = reinterpret_cast<__nv_bfloat162*>(&sv);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        sp[j] = __floats2bfloat162_rn(__low2float(xp[j]) + __low2float(bp[j]), __high2float(xp[j]) + __high2float(bp[j]));
+        sp[j] = __hadd2_rn(xp[j], bp[j]);  // the 32-bit sum of two bfloat16 values, rounded once
         f[2 * j] = __low2float(sp[j]);
         f[2 * j + 1] = __high2float(sp[j]);
       }
@@ -131,10 +131,17 @@ __global__ void rmsnorm_bf16x8_kernel(bf16* __restrict__ out, bf16* x_new, const
   if (on) {
     uint4 ov;
     __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+    if (gain_f32) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      op[j] = __floats2bfloat162_rn(round_to<bf16>(f[2 * j] * rstd) * load_gain<bf16>(gain, k + 2 * j, gain_f32),
-                                    round_to<bf16>(f[2 * j + 1] * rstd) * load_gain<bf16>(gain, k + 2 * j + 1, gain_f32));
+      for (int j = 0; j < 4; ++j)
+        op[j] = __floats2bfloat162_rn(round_to<bf16>(f[2 * j] * rstd) * load_gain<bf16>(gain, k + 2 * j, 1),
+                                      round_to<bf16>(f[2 * j + 1] * rstd) * load_gain<bf16>(gain, k + 2 * j + 1, 1));
+    } else {
+      const uint4 gv = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(gain) + k);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        op[j] = __hmul2_rn(__floats2bfloat162_rn(f[2 * j] * rstd, f[2 * j + 1] * rstd), reinterpret_cast<const __nv_bfloat162*>(&gv)[j]);
+    }
     *reinterpret_cast<uint4*>(out + base + k) = ov;
   }
 }
@@ -143,7 +150,7 @@ template <typename T>
 int launch_rmsnorm(void* out, void* x_new, const void* x, const void* branch, const void* gain, int gain_f32, int rows,
                    int H, float eps, cudaStream_t stream) {
   if (rows == 0) return 0;
-  if (sizeof(T) == 2 && H % 8 == 0 && H <= 8192) {
+  if (sizeof(T) == 2 && H % 8 == 0 && H <= 8192 && (gain_f32 || ((uintptr_t)gain & 15) == 0)) {  // 16-byte gain loads
     const int threads = ((H / 8 + 31) / 32) * 32;
     return (int)launch_pdl(rmsnorm_bf16x8_kernel, dim3(rows), dim3(threads), 0, stream, (bf16*)out, (bf16*)x_new,
                            (const bf16*)x, (const bf16*)branch, gain, gain_f32, H, eps);
@@ -194,13 +201,14 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
   out[r * I + i] = from_float<T>(s * u);
 }
 
-// bfloat16, I a multiple of 8: eight gate and eight up values per thread
-__global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, int I, long long n_pieces) {
-  const long long piece = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (piece >= n_pieces) return;
-  const int per_row = I / 8;
-  const long long r = piece / per_row;
-  const int i = (int)(piece % per_row) * 8;
+// bfloat16, I a multiple of 8: eight gate and eight up values per thread; blockIdx.x is the row.
+// silu runs in 32-bit with the fast exponential and reciprocal (a few units in the last place of a float,
+// far below the bfloat16 rounding that follows); the product of the two rounded factors is one packed
+// bfloat16 multiply, which rounds the exact product as the unpacked form does.
+__global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, int I) {
+  const size_t r = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= I) return;
   const uint4 gv = *reinterpret_cast<const uint4*>(gu + r * 2 * I + i);
   const uint4 uv = *reinterpret_cast<const uint4*>(gu + r * 2 * I + I + i);
   const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
@@ -210,8 +218,8 @@ __global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restr
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float g0 = __low2float(gp[j]), g1 = __high2float(gp[j]);
-    const float s0 = round_to<bf16>(g0 / (1.0f + expf(-g0))), s1 = round_to<bf16>(g1 / (1.0f + expf(-g1)));
-    op[j] = __floats2bfloat162_rn(s0 * __low2float(up[j]), s1 * __high2float(up[j]));
+    const __nv_bfloat162 silu = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
+    op[j] = __hmul2_rn(silu, up[j]);
   }
   *reinterpret_cast<uint4*>(out + r * I + i) = ov;
 }
@@ -237,10 +245,9 @@ KRK_API int krk_gather_rows(void* out, const void* table, const int* ids, int ro
 KRK_API int krk_swiglu(void* out, const void* gu, int rows, int I, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (dtype == KRK_DTYPE_BF16 && I % 8 == 0) {
-    const long long pieces = (long long)rows * (I / 8);
-    const long long blocks = (pieces + 255) / 256;
-    if (blocks > 0x7fffffffLL) return -3;
-    swiglu_bf16x8_kernel<<<(unsigned)blocks, 256, 0, stream>>>((bf16*)out, (const bf16*)gu, I, pieces);
+    const int chunks = (I / 8 + 255) / 256;
+    if (chunks > 65535) return -3;
+    swiglu_bf16x8_kernel<<<dim3(rows, chunks), 256, 0, stream>>>((bf16*)out, (const bf16*)gu, I);
     KRK_CHECK_LAUNCH();
     return 0;
   }

@@ -230,6 +230,33 @@ def test_rope_write_then_attention_prefill_and_decode(ops, dtype, shape, window)
         close(got, want, dtype, f"attention, step {s}, shape {shape}, window {window}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(3, 1, 16), (6, 2, 32), (8, 8, 64), (32, 8, 128), (7, 1, 128), (2, 1, 256), (5, 1, 48)])
+def test_rope_write_many_rows(ops, dtype, shape):
+    """Steps with hundreds of rows take the block-per-row kernel (bfloat16, head sizes 16..256 in powers of
+    two); every row's position, page and head must come out as with few rows."""
+    heads, kv_heads, D = shape
+    ref = TorchOps(dtype)
+    width, n_slots = 8, 4
+    cache = make_cache(40, kv_heads, D, n_slots, width, dtype, 23)
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.k, ref_cache.v = cache.k.clone(), cache.v.clone()
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    qg = (1.5 + 0.1 * rand((D,), torch.float32, 24)).to(dtype)
+    kg = (0.7 + 0.1 * rand((D,), torch.float32, 25)).to(dtype)
+    batch = make_batch([1, 3, 0], [37, 0, 130], [200, 90, 41])
+    qkv = rand((batch.n_rows, (heads + 2 * kv_heads) * D), dtype, 26, 1.0)
+    qkv_ref = qkv.clone()
+    ops.qk_norm_rope_write(qkv, heads, kv_heads, D, qg, kg, 1e-5, cos, sin, batch, cache)
+    ref.qk_norm_rope_write(qkv_ref, heads, kv_heads, D, qg, kg, 1e-5, cos, sin, batch, ref_cache)
+    close(qkv[:, :heads * D], qkv_ref[:, :heads * D], dtype, "rotated queries")
+    close(cache.k, ref_cache.k, dtype, "key pages")
+    assert torch.equal(cache.v, ref_cache.v), "values are copied raw"
+    assert torch.equal(qkv[:, heads * D:], qkv_ref[:, heads * D:]), "the step's own k and v columns stay as they were"
+
+
 @pytest.mark.parametrize("shape", ATTN_SHAPES + [(40, 2, 64)])
 @pytest.mark.parametrize("window", [None, 70])
 @pytest.mark.parametrize("n_seqs", [1, 3, 40])
