@@ -1,27 +1,30 @@
 // Causal grouped-query attention for steps that bring many tokens per sequence, on the
-// 5th-generation tensor cores: S = Q K^T and O_j = P V run as tcgen05.mma with their results
-// in tensor memory; K and V pages arrive by TMA; the softmax runs in four warps, one query
-// row per thread.
+// 5th-generation tensor cores. A block owns two query tiles of 128 rows that share every K and V
+// page it reads; S = Q K^T, P and O all live in tensor memory:
+//
+//   tensor memory (512 columns): S0 | S1 | O0 | O1. P_t, rounded to bfloat16, overwrites the first
+//   64 columns of S_t (two keys per 32-bit column) and is the A operand of O_t += P_t V.
+//   shared memory: Q0, Q1, and K and V double-buffered (128-byte swizzle, filled by TMA).
+//
+// Warps 0..3 run the softmax of tile 0, warps 4..7 that of tile 1 (thread = query row = tensor-memory
+// lane); lane 0 of warp 8 issues every TMA load and every MMA, in the order
+//   ... PV0(j-1) QK0(j) PV1(j-1) QK1(j) PV0(j) QK0(j+1) ...
+// so that while one tile's rows are in the softmax the tensor core works for the other tile.
+// Per key block of 128 keys (two cache pages) and tile:
+//   S = Q K^T                                   [issuer]   -> s_full
+//   row max; p = exp2(S*c - m) rounded to bfloat16 -> tensor memory  [softmax]  -> p_ready
+//   O += P V   (V as an MN-major B operand)     [issuer]
+// O stays in tensor memory across key blocks. The reference maximum m of a row moves only when the
+// row's maximum has grown by more than 2^8 since it was set (then the warp rescales its O rows in
+// tensor memory); until then p <= 2^8, which float32 sums and bfloat16 probabilities hold without
+// loss. The final division by the row's sum undoes the choice of m exactly as with a running maximum.
 //
 // Numerics as in the other attention kernels of this library (and the reference's,
-// engine/kernels/attention.py:9-11,104-122 of willzeng274/kernel-rush-kawk): scores and
-// running max / sum in float32, probabilities rounded to bfloat16 before P.V, the output
-// accumulated in float32 (here in registers, one row per thread) and divided by the sum once
-// at the end. A query at position p sees keys max(0, p - window + 1)..p. The rows of a tile
-// are (token, group member) pairs of one kv head, row R -> token R / G, head kh * G + R % G,
-// so all G query heads of a kv head share one read of K and V (attention.py:70-73).
-//
-// Block = 160 threads. Warps 0..3: softmax and output accumulation, thread t owns row t and
-// tensor-memory lane t. Warp 4: allocates tensor memory; its lane 0 issues TMA loads and MMAs.
-// Per key block of 128 keys (two cache pages):
-//   TMA K, V -> shared memory (128-byte swizzle)             [issuer]
-//   S = Q K^T          (tcgen05.mma, K-major A and B)          [issuer]   -> s_full
-//   p = exp2(S*c - m)  rounded to bfloat16, written to shared
-//       memory over the K tile, which S no longer needs        [softmax]  -> p_ready
-//   O_j = P V          (tcgen05.mma, V as an MN-major B)       [issuer]   -> o_full
-//   o = o * alpha + O_j (tcgen05.ld)                           [softmax]
-// Two blocks share an SM (96 KB of shared memory and 256 tensor-memory columns each at head
-// size 128), so one block's softmax overlaps the other's MMAs. Every barrier wait is bounded.
+// engine/kernels/attention.py:9-11,104-122 of willzeng274/kernel-rush-kawk): scores, maxima and sums
+// in float32, probabilities rounded to bfloat16 before P.V, the output accumulated in float32. A
+// query at position p sees keys max(0, p - window + 1)..p. The rows of a tile are (token, group
+// member) pairs of one kv head, row R -> token R / G, head kh * G + R % G, so all G query heads of a
+// kv head share one read of K and V (attention.py:70-73). Every barrier wait is bounded.
 //
 // Compiled once per head size, for head sizes 64 and 128: -DKRK_HEAD_DIM=<D>.
 #include "tcgen05.cuh"
@@ -37,15 +40,19 @@ namespace {
 using namespace tc;
 
 constexpr int D = KRK_HEAD_DIM;
-constexpr int ROWS = 128;              // query rows per block
+constexpr int ROWS = 128;              // query rows per tile
+constexpr int PAIR = 2 * ROWS;         // query rows per block
 constexpr int KEYS = 128;              // keys per block iteration: two pages
 constexpr int DB = D / 64;             // 64-wide blocks of the head dimension
-constexpr int THREADS = 160;
+constexpr int THREADS = 288;           // 2 x 4 softmax warps + the issuing warp
 constexpr uint32_t SUB = 128 * 128;    // bytes of a [128 rows x 64 bf16] swizzled sub-tile
-constexpr uint32_t Q_BYTES = DB * SUB, K_BYTES = DB * SUB, V_BYTES = DB * SUB, P_BYTES = 2 * SUB;
-constexpr uint32_t KP_BYTES = K_BYTES > P_BYTES ? K_BYTES : P_BYTES;  // P overwrites K
-constexpr uint32_t TMEM_COLS = (128 + D) <= 256 ? 256 : 512;
+constexpr uint32_t TILE_BYTES = DB * SUB;  // a Q, K or V tile
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_O = 256;       // O_t starts at column 256 + t * D; S_t at t * 128
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.f;    // in log2 units: the reference maximum moves when outgrown by 2^8
+
+enum Bar { K_FULL = 0, V_FULL = 2, K_FREE = 4, V_FREE = 6, S_FULL = 8, P_READY = 10, O_DONE = 12, N_BARS = 14 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -56,7 +63,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // byte offset of the 16-byte piece `chunk` (8 elements) of row `r` inside a swizzled [128 x 64] sub-tile
 __device__ __forceinline__ uint32_t swz(int r, int chunk) { return (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4); }
 
-__global__ void __launch_bounds__(THREADS, 2)
+struct TileRange {
+  int lo, hi;  // key blocks the tile can see; lo > hi: the tile has no rows
+  __device__ __forceinline__ bool has(int j) const { return j >= lo && j <= hi; }
+};
+
+__device__ __forceinline__ TileRange tile_range(int row_begin, int n_rows, int G, int q_len, int start, int window) {
+  TileRange t;
+  if (row_begin >= n_rows) { t.lo = 1; t.hi = 0; return t; }
+  const int first_tok = row_begin / G;
+  const int last_tok = min(q_len - 1, (row_begin + ROWS - 1) / G);
+  t.lo = window > 0 ? max(0, start + first_tok - window + 1) / KEYS : 0;
+  t.hi = (start + last_tok) / KEYS;
+  return t;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
@@ -64,207 +86,266 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                          int width, float scale_log2, int window, int* __restrict__ error) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;
-  unsigned char* k_s = q_s + Q_BYTES;   // K, then P
-  unsigned char* v_s = k_s + KP_BYTES;
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(v_s + V_BYTES);
-  uint64_t* s_full = kv_full + 1;
-  uint64_t* p_ready = kv_full + 2;
-  uint64_t* o_full = kv_full + 3;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_full + 4);
+  unsigned char* q_s = base;                    // two tiles
+  unsigned char* k_s = q_s + 2 * TILE_BYTES;    // two stages
+  unsigned char* v_s = k_s + 2 * TILE_BYTES;    // two stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
 
-  // blockIdx.x counts (tile, kv head) pairs with the tile as the slow index, descending: blocks start in
-  // launch order, so the tiles with the most key blocks, of every kv head, run first and the short ones
+  // blockIdx.x counts (row pair, kv head) with the pair as the slow index, descending: blocks start in
+  // launch order, so the pairs with the most key blocks, of every kv head, run first and the short ones
   // fill the tail
   const int seq = blockIdx.y, kh = blockIdx.x % HKV;
-  const int tile = gridDim.x / HKV - 1 - blockIdx.x / HKV;
+  const int pair = gridDim.x / HKV - 1 - blockIdx.x / HKV;
   const int G = HQ / HKV;
   const int q_len = seq_qlen[seq];
   const int n_rows = q_len * G;
-  if (tile * ROWS >= n_rows) return;
+  if (pair * PAIR >= n_rows) return;
   const int start = seq_start[seq], slot = seq_slot[seq], row0 = cu_q[seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
-    mbar_init(o_full, 1);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tmem_slot[1] = (uint32_t)*reinterpret_cast<volatile int*>(error);  // a block that gave up: the others do no work
   }
-  if (warp == 4) {
+  if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // the query tile: row r, 16-byte piece c -> swizzled K-major sub-tiles; rows past the end are zero
-  for (int i = threadIdx.x; i < ROWS * (D / 8); i += THREADS) {
+  // the query tiles: row r, 16-byte piece c -> swizzled K-major sub-tiles; rows past the end are zero
+  for (int i = threadIdx.x; i < PAIR * (D / 8); i += THREADS) {
     const int r = i / (D / 8), c = i % (D / 8);
-    const int R = tile * ROWS + r;
+    const int R = pair * PAIR + r;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (R < n_rows) v = *reinterpret_cast<const uint4*>(qkv + (size_t)(row0 + R / G) * q_stride + (size_t)(kh * G + R % G) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + (c / 8) * SUB + swz(r, c % 8)) = v;
+    *reinterpret_cast<uint4*>(q_s + (r / ROWS) * TILE_BYTES + (c / 8) * SUB + swz(r % ROWS, c % 8)) = v;
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_s = *tmem_slot;        // S: columns 0..127
-  const uint32_t tmem_o = tmem_s + 128;      // O_j: columns 128..128+D-1
+  const uint32_t tmem = *tmem_slot;
+  const bool dead = tmem_slot[1] != 0;
 
-  // key blocks this tile can see
-  const int first_tok = (tile * ROWS) / G;
-  const int last_tok = min(q_len - 1, (tile * ROWS + ROWS - 1) / G);
-  const int jb_lo = window > 0 ? max(0, start + first_tok - window + 1) / KEYS : 0;
-  const int jb_hi = (start + last_tok) / KEYS;
+  const TileRange r0 = tile_range(pair * PAIR, n_rows, G, q_len, start, window);
+  const TileRange r1 = tile_range(pair * PAIR + ROWS, n_rows, G, q_len, start, window);
+  const int j_lo = r0.lo;                                   // tile 0 exists and starts no later than tile 1
+  const int j_hi = r1.lo <= r1.hi ? max(r0.hi, r1.hi) : r0.hi;
+  const int n = j_hi - j_lo + 1;
 
-  if (warp == 4) {
+  if (dead) {
+    // nothing to do
+  } else if (warp == 8) {
     if (lane == 0) {
       // ---- issuer: TMA loads and MMAs ----
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KEYS >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       bool ok = true;
-      for (int jb = jb_lo; jb <= jb_hi && ok; ++jb) {
-        const uint32_t it = (uint32_t)(jb - jb_lo);
-        if (it > 0 && !mbar_wait(o_full, (it - 1) & 1)) { atomicExch(error, 6); ok = false; break; }  // K/P and V are free
-        mbar_expect_tx(kv_full, K_BYTES + V_BYTES);
+      auto give_up = [&](int code) { atomicExch(error, code); ok = false; };
+      auto load_tile = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int i) {
+        mbar_expect_tx(bar, TILE_BYTES);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int page = table[(size_t)slot * width + (2 * jb + half) % width];
+          const int page = table[(size_t)slot * width + (2 * (j_lo + i) + half) % width];
           const int row = (page * HKV + kh) * KRK_PAGE;
 #pragma unroll
-          for (int h = 0; h < DB; ++h) {
-            tma_load_2d(k_s + h * SUB + half * (64 * 128), &map_k, kv_full, h * 64, row);
-            tma_load_2d(v_s + h * SUB + half * (64 * 128), &map_v, kv_full, h * 64, row);
-          }
+          for (int h = 0; h < DB; ++h) tma_load_2d(dst + h * SUB + half * (64 * 128), map, bar, h * 64, row);
         }
-        if (!mbar_wait(kv_full, it & 1)) { atomicExch(error, 7); ok = false; break; }
-        tc_fence_after();
+      };
+      auto load_k = [&](int i) { load_tile(k_s + (i & 1) * TILE_BYTES, &map_k, bars + K_FULL + (i & 1), i); };
+      auto load_v = [&](int i) { load_tile(v_s + (i & 1) * TILE_BYTES, &map_v, bars + V_FULL + (i & 1), i); };
+      auto qk = [&](int t, int i) {  // S_t = Q_t K_i^T
+        const unsigned char* q = q_s + t * TILE_BYTES;
+        const unsigned char* k = k_s + (i & 1) * TILE_BYTES;
 #pragma unroll
         for (int h = 0; h < DB; ++h)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_s, umma_desc_sw128(q_s + h * SUB + kk * 32, 16, 1024),
-                      umma_desc_sw128(k_s + h * SUB + kk * 32, 16, 1024), idesc_s, (h > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait(p_ready, it & 1)) { atomicExch(error, 8); ok = false; break; }
-        tc_fence_after();
+            umma_bf16(tmem + t * 128, umma_desc_sw128(q + h * SUB + kk * 32, 16, 1024),
+                      umma_desc_sw128(k + h * SUB + kk * 32, 16, 1024), idesc_s, (h > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bars + S_FULL + t);
+      };
+      auto pv = [&](int t, int i, bool first) {  // O_t (+)= P_t V_i, 16 keys (8 columns of P) per instruction
+        const unsigned char* v = v_s + (i & 1) * TILE_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < KEYS / 16; ++ks)  // 16 keys per instruction
-          umma_bf16(tmem_o, umma_desc_sw128(k_s + (ks / 4) * SUB + (ks % 4) * 32, 16, 1024),
-                    umma_desc_sw128(v_s + ks * 16 * 128, SUB, 1024), idesc_o, ks > 0 ? 1u : 0u);
-        umma_commit(o_full);
+        for (int ks = 0; ks < KEYS / 16; ++ks)
+          umma_bf16_tmem_a(tmem + TMEM_O + t * D, tmem + t * 128 + ks * 8, umma_desc_sw128(v + ks * 16 * 128, SUB, 1024),
+                           idesc_o, (first && ks == 0) ? 0u : 1u);
+      };
+      const TileRange rng[2] = {r0, r1};
+      load_k(0);
+      load_v(0);
+      if (n > 1) load_k(1);
+      if (!mbar_wait(bars + K_FULL, 0)) give_up(6);
+      if (ok) {
+        tc_fence_after();
+        if (r0.has(j_lo)) qk(0, 0);
+        if (r1.has(j_lo)) qk(1, 0);
+        umma_commit(bars + K_FREE);
+      }
+      for (int i = 0; i < n && ok; ++i) {
+        const int j = j_lo + i, b = i & 1;
+        if (i + 1 < n) {  // V of the next block goes where block i - 1's was
+          if (i >= 1 && !mbar_wait(bars + V_FREE + ((i + 1) & 1), ((i - 1) >> 1) & 1)) { give_up(7); break; }
+          load_v(i + 1);
+        }
+        bool v_ready = false, k_ready = false;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (rng[t].has(j)) {
+            if (!mbar_wait(bars + P_READY + t, (j - rng[t].lo) & 1)) { give_up(8); break; }
+            if (!v_ready) {
+              if (!mbar_wait(bars + V_FULL + b, (i >> 1) & 1)) { give_up(9); break; }
+              v_ready = true;
+            }
+            tc_fence_after();
+            pv(t, i, j == rng[t].lo);
+            if (j == rng[t].hi) umma_commit(bars + O_DONE + t);
+          }
+          if (t == 1) umma_commit(bars + V_FREE + b);
+          if (i + 1 < n) {
+            if (rng[t].has(j + 1)) {
+              if (!k_ready) {
+                if (!mbar_wait(bars + K_FULL + ((i + 1) & 1), ((i + 1) >> 1) & 1)) { give_up(10); break; }
+                k_ready = true;
+              }
+              tc_fence_after();
+              qk(t, i + 1);
+            }
+            if (t == 1) umma_commit(bars + K_FREE + ((i + 1) & 1));
+          }
+        }
+        if (ok && i + 2 < n) {  // K of block i + 2 goes where block i's was
+          if (!mbar_wait(bars + K_FREE + b, (i >> 1) & 1)) { give_up(11); break; }
+          load_k(i + 2);
+        }
       }
     }
   } else {
-    // ---- softmax and accumulation: thread t owns row t ----
-    const int r = threadIdx.x;
-    const int R = tile * ROWS + r;
+    // ---- softmax: thread = row of tile t ----
+    const int t = warp >> 2;
+    const TileRange rng = t == 0 ? r0 : r1;
+    const int r = threadIdx.x - t * ROWS;
+    const int R = pair * PAIR + t * ROWS + r;
     const bool valid = R < n_rows;
     const int tok = valid ? R / G : 0;
     const int pos = valid ? start + tok : -1;  // -1: sees nothing
     const int lo = (valid && window > 0) ? max(0, pos - window + 1) : 0;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem + t * 128 + lane_addr;
+    const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
     float m = -INFINITY, l = 0.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
     bool ok = true;
-    for (int jb = jb_lo; jb <= jb_hi && ok; ++jb) {
-      const uint32_t it = (uint32_t)(jb - jb_lo);
-      const int key0 = jb * KEYS;
-      if (!mbar_wait(s_full, it & 1)) { if (lane == 0) atomicExch(error, 9); ok = false; break; }
+    for (int j = rng.lo; j <= rng.hi; ++j) {
+      const uint32_t c = (uint32_t)(j - rng.lo);
+      const int key0 = j * KEYS;
+      // tensor-memory loads and stores are warp-wide: the whole warp gives up together
+      if (!__all_sync(0xffffffffu, mbar_wait(bars + S_FULL + t, c & 1))) { if (lane == 0) atomicExch(error, 12); ok = false; break; }
       tc_fence_after();
+      uint32_t s[KEYS];
+#pragma unroll
+      for (int q = 0; q < KEYS / 32; ++q) tmem_ld_32x32(tmem_s + 32 * q, *reinterpret_cast<uint32_t(*)[32]>(s + 32 * q));
+      tmem_wait_ld();
       const bool whole = key0 + KEYS - 1 <= pos && key0 >= lo;  // the row sees every key of the block
-      // pass 1: the row's maximum
       float mx = -INFINITY;
+      if (whole) {
 #pragma unroll
-      for (int c0 = 0; c0 < KEYS; c0 += 32) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c0, s);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (whole) {
+        for (int i = 0; i < KEYS; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+      } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(s[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c0 + j;
-            if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(s[j]));
-          }
+        for (int i = 0; i < KEYS; ++i) {
+          const int key = key0 + i;
+          if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(s[i]));
         }
       }
       const float m_new = fmaxf(m, mx * scale_log2);
-      const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2(m - m_safe);
-      // pass 2: probabilities, their sum, P into shared memory (over the K tile)
-      float sum = 0.f;
+      const bool outgrown = m != -INFINITY && m_new - m > RESCALE_STEP;
+      if (__any_sync(0xffffffffu, outgrown)) {
+        // the warp moves its rows' reference maxima; the block's P.V has not been issued and the one before
+        // it is complete (S of this block came after it), so nothing else touches these rows of O
+        const float alpha = m == -INFINITY ? 1.f : fast_exp2(m - m_new);
 #pragma unroll
-      for (int c0 = 0; c0 < KEYS; c0 += 32) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c0, s);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        float p[32];
-        if (whole) {
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_o + c0, o);
+          tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) p[j] = fast_exp2(fmaf(__uint_as_float(s[j]), scale_log2, -m_safe));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c0 + j;
-            p[j] = (key <= pos && key >= lo) ? fast_exp2(fmaf(__uint_as_float(s[j]), scale_log2, -m_safe)) : 0.f;
-          }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(tmem_o + c0, o);
         }
+        l *= alpha;
+        m = m_new;
+      } else if (m == -INFINITY) {
+        m = m_new;  // no key seen before this block: O and l are still zero
+      }
+      const float m_safe = m == -INFINITY ? 0.f : m;
+      float sum = 0.f;
+      uint32_t pk[KEYS / 2];
+      if (whole) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) sum += p[j];
+        for (int i = 0; i < KEYS; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe));
+          sum += p0 + p1;
+          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      } else {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {  // four 16-byte pieces of 8 keys
-          uint4 pk;
-          __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) pp[e] = __floats2bfloat162_rn(p[8 * q + 2 * e], p[8 * q + 2 * e + 1]);
-          const int chunk = (c0 + 8 * q) / 8;  // 0..15 over the 128 keys
-          *reinterpret_cast<uint4*>(k_s + (chunk / 8) * SUB + swz(r, chunk % 8)) = pk;
+        for (int i = 0; i < KEYS; i += 2) {
+          const int key = key0 + i;
+          const float p0 = (key <= pos && key >= lo) ? fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe)) : 0.f;
+          const float p1 = (key + 1 <= pos && key + 1 >= lo) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe)) : 0.f;
+          sum += p0 + p1;
+          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
         }
       }
-      l = l * alpha + sum;
-      m = m_new;
-      fence_async_smem();
+      l += sum;
+      __syncwarp();  // rows that see the whole block and rows at its edge took different paths
+#pragma unroll
+      for (int q = 0; q < KEYS / 64; ++q) tmem_st_32x32(tmem_s + 32 * q, *reinterpret_cast<const uint32_t(*)[32]>(pk + 32 * q));
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_ready);
-      if (!mbar_wait(o_full, it & 1)) { if (lane == 0) atomicExch(error, 10); ok = false; break; }
+      mbar_arrive(bars + P_READY + t);
+    }
+    if (ok && rng.lo <= rng.hi) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bars + O_DONE + t, 0))) { if (lane == 0) atomicExch(error, 13); ok = false; }
       tc_fence_after();
+    }
+    if (ok && rng.lo <= rng.hi) {  // the whole warp reads tensor memory; rows past the end store nothing
+      const float inv = valid ? 1.0f / l : 0.f;
+      bf16* dst = out + (size_t)(row0 + tok) * HQ * D + (size_t)(kh * G + (valid ? R % G : 0)) * D;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t t[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c0, t);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_o + c0, o);
+        tmem_wait_ld();
+        if (valid) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * alpha + __uint_as_float(t[j]);
-      }
-      tc_fence_before();
-    }
-    if (valid && ok) {
-      const float inv = 1.0f / l;
-      bf16* dst = out + (size_t)(row0 + tok) * HQ * D + (size_t)(kh * G + R % G) * D;
+          for (int c = 0; c < 32; c += 8) {
+            uint4 pk;
+            __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint4 pk;
-        __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) pp[e] = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + c) = pk;
+            for (int e = 0; e < 4; ++e)
+              pp[e] = __floats2bfloat162_rn(__uint_as_float(o[c + 2 * e]) * inv, __uint_as_float(o[c + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + c) = pk;
+          }
+        }
+        __syncwarp();
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
 }
 
-constexpr size_t SMEM_BYTES = Q_BYTES + KP_BYTES + V_BYTES + 1024 + 64;
+constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64;
 
 }  // namespace
 
@@ -277,7 +358,7 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
                                           int window, int* error, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
   const int G = HQ / HKV;
-  const long long tiles = ((long long)max_q_len * G + ROWS - 1) / ROWS;
+  const long long tiles = ((long long)max_q_len * G + PAIR - 1) / PAIR;
   if (tiles * HKV > 0x7fffffffLL || n_seqs > 65535) return -3;
   if ((q_stride % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return -2;
   CUtensorMap map_k, map_v;
