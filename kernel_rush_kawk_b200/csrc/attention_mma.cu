@@ -509,16 +509,43 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   // "I have started": waited for only before the first write into another block's shared memory
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   grid_launch_dependents();
-  grid_dependency_wait();
-  KRK_TRACE_READY
   const int n_splits = cluster.num_blocks(), split = cluster.block_rank();
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
   const int seq = blockIdx.z;
   const int G = HQ / HKV;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  int pos = seq_start[seq];
-  const int slot = seq_slot[seq];
+  // What the kernel before this one does not write is read before the wait on it: the step's positions and
+  // slots (uploaded, or written by the selection kernel, which lets no later kernel start before it has
+  // ended), the page table, and the pages of earlier tokens, whose copies travel while that kernel finishes.
+  int pos = __ldcg(seq_start + seq);
+  const int slot = __ldcg(seq_slot + seq);
+  if (pos < 0 || pos >= n_pos) {  // flagged and clamped: never an access out of range
+    if (threadIdx.x == 0 && error) atomicExch(error, 2);
+    pos = max(0, min(pos, n_pos - 1));
+  }
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
+  const int n_blocks = j_last - j_first + 1;
+  const int per = (n_blocks + n_splits - 1) / n_splits;
+  const int j_lo = j_first + split * per, j_hi = min(j_last, j_lo + per - 1);
+  const bool owns_new = j_lo <= j_last && j_last <= j_hi;  // this block's keys include the new token's
+
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+  const size_t head_off = (size_t)kh * KRK_PAGE * D;
+  auto issue = [&](int j) {  // page j of this block's range into stage (j - j_lo) % FSTAGES; one group per call
+    if (j <= j_hi) {
+      const int page = table[(size_t)slot * width + j % width];
+      bf16* ks = smem + (size_t)((j - j_lo) % FSTAGES) * 2 * TILE_ELEMS;
+      load_page(ks, k_cache + (size_t)page * page_stride + head_off);
+      load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < FSTAGES - 1; ++i) issue(j_lo + i);
+  grid_dependency_wait();
+  KRK_TRACE_READY
 
   // The new token's rows. Warp w takes query rows w, w + 4, ... of this tile (rows beyond G
   // are zero); the key and value rows go to the warp with the fewest query rows, in every
@@ -547,37 +574,12 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     }
   }
 
-  if (pos < 0 || pos >= n_pos) {  // flagged and clamped: never an access out of range
-    if (threadIdx.x == 0 && error) atomicExch(error, 2);
-    pos = max(0, min(pos, n_pos - 1));
-  }
   const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
   const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i)
     if (warp + 4 * i < q_rows) regs[i].load_angles(cos_row, sin_row, lane);
   if (warp == k_warp) k_regs.load_angles(cos_row, sin_row, lane);
-
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
-  const int n_blocks = j_last - j_first + 1;
-  const int per = (n_blocks + n_splits - 1) / n_splits;
-  const int j_lo = j_first + split * per, j_hi = min(j_last, j_lo + per - 1);
-  const bool owns_new = j_lo <= j_last && j_last <= j_hi;  // this block's keys include the new token's
-
-  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
-  const size_t head_off = (size_t)kh * KRK_PAGE * D;
-  auto issue = [&](int j) {  // page j of this block's range into stage (j - j_lo) % FSTAGES; one group per call
-    if (j <= j_hi) {
-      const int page = table[(size_t)slot * width + j % width];
-      bf16* ks = smem + (size_t)((j - j_lo) % FSTAGES) * 2 * TILE_ELEMS;
-      load_page(ks, k_cache + (size_t)page * page_stride + head_off);
-      load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
-    }
-    cp_async_commit();
-  };
-#pragma unroll
-  for (int i = 0; i < FSTAGES - 1; ++i) issue(j_lo + i);  // the cache pages travel while the new token is prepared
 
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i) {

@@ -77,7 +77,8 @@ __global__ void select_scan_kernel(unsigned long long* __restrict__ packed, cons
 __global__ void select_finish_kernel(int* __restrict__ tokens, unsigned long long* __restrict__ packed, int rows,
                                      int* __restrict__ feed_tokens, int* __restrict__ feed_pos,
                                      int* __restrict__ feed_start) {
-  grid_launch_dependents();
+  // No early start for the kernels behind this one: it writes the next step's tokens and positions, and
+  // kernels of that step read the positions before their own wait on their predecessor.
   grid_dependency_wait();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
