@@ -33,7 +33,15 @@ constexpr int DP = D + 8;            // shared-memory row pitch (elements): 16 b
 constexpr int KSTEPS = D / 16;       // k-steps of Q.K^T
 constexpr int DTILES = D / 8;        // n-tiles of P.V
 constexpr int THREADS = 128;
-constexpr int TILE_ELEMS = KRK_PAGE * DP;
+// A page of keys or values in shared memory. Where a row is a power-of-two number (at least eight) of
+// 16-byte pieces, rows are packed and piece c of key k sits at piece c ^ (k & 7), which spreads the eight
+// rows of an ldmatrix over all banks without padding; other head sizes pad each row by 16 bytes instead.
+constexpr bool KV_SWIZZLE = (D == 64 || D == 128 || D == 256);
+constexpr int KVP = KV_SWIZZLE ? D : DP;  // row pitch of a page in shared memory (elements)
+constexpr int TILE_ELEMS = KRK_PAGE * KVP;
+__device__ __forceinline__ int kv_off(int key, int piece) {
+  return key * KVP + ((KV_SWIZZLE ? (piece ^ (key & 7)) : piece) << 3);
+}
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Copy one page [64][D] of one kv head to shared memory [64][DP], all threads of the block.
@@ -41,7 +49,7 @@ __device__ __forceinline__ void load_page(bf16* dst, const bf16* __restrict__ sr
   constexpr int CHUNKS = KRK_PAGE * (D / 8);
   for (int i = threadIdx.x; i < CHUNKS; i += THREADS) {
     const int key = i / (D / 8), ch = i % (D / 8);
-    cp_async_16(dst + key * DP + ch * 8, src + key * D + ch * 8);
+    cp_async_16(dst + kv_off(key, ch), src + key * D + ch * 8);
   }
 }
 
@@ -58,7 +66,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&
 #pragma unroll
     for (int n = 0; n < NTILES; n += 2) {
       uint32_t b0, b1, b2, b3;
-      const bf16* p = ks + (key0 + n * 8 + ((lane >> 4) << 3) + (lane & 7)) * DP + kk * 16 + ((lane >> 3) & 1) * 8;
+      const bf16* p = ks + kv_off(key0 + n * 8 + ((lane >> 4) << 3) + (lane & 7), kk * 2 + ((lane >> 3) & 1));
       ldmatrix_x4(b0, b1, b2, b3, p);
       mma_bf16_16816(s[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
       mma_bf16_16816(s[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
@@ -79,7 +87,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[
 #pragma unroll
     for (int n = 0; n < DTILES; n += 2) {
       uint32_t b0, b1, b2, b3;
-      const bf16* q = vs + (key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + n * 8 + (lane >> 4) * 8;
+      const bf16* q = vs + kv_off(key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n + (lane >> 4));
       ldmatrix_x4_trans(b0, b1, b2, b3, q);
       mma_bf16_16816(o[n], a0, a1, a2, a3, b0, b1);
       mma_bf16_16816(o[n + 1], a0, a1, a2, a3, b2, b3);
@@ -632,8 +640,8 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     bf16* vs = ks + TILE_ELEMS;
     if (j == j_last) {  // the page in shared memory predates this step's write: put the new row in
       for (int i = threadIdx.x; i < D; i += THREADS) {
-        ks[(pos % KRK_PAGE) * DP + i] = kv_new[i];
-        vs[(pos % KRK_PAGE) * DP + i] = kv_new[D + i];
+        ks[kv_off(pos % KRK_PAGE, i >> 3) + (i & 7)] = kv_new[i];
+        vs[kv_off(pos % KRK_PAGE, i >> 3) + (i & 7)] = kv_new[D + i];
       }
       __syncthreads();
     }

@@ -504,16 +504,16 @@ __device__ __forceinline__ void attention_item(const Args& a, const Layer& d, co
         const int p = threadIdx.x + i * ATT_THREADS;
         if (p < PAGE_PIECES) {
           const int key = p / (D / 8), ch = p % (D / 8);
-          *reinterpret_cast<uint4*>(ks + key * DP + ch * 8) = kreg[i];
-          *reinterpret_cast<uint4*>(vs + key * DP + ch * 8) = vreg[i];
+          *reinterpret_cast<uint4*>(ks + kv_off(key, ch)) = kreg[i];
+          *reinterpret_cast<uint4*>(vs + kv_off(key, ch)) = vreg[i];
         }
       }
     }
     __syncthreads();
     if (j == j_last) {  // the row of the new token, whether or not the global write has landed
       for (int i = threadIdx.x; i < D; i += NTHREADS) {
-        ks[(pos % KRK_PAGE) * DP + i] = as.kv_new[i];
-        vs[(pos % KRK_PAGE) * DP + i] = as.kv_new[D + i];
+        ks[kv_off(pos % KRK_PAGE, i >> 3) + (i & 7)] = as.kv_new[i];
+        vs[kv_off(pos % KRK_PAGE, i >> 3) + (i & 7)] = as.kv_new[D + i];
       }
       __syncthreads();
     }
