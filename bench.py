@@ -257,7 +257,7 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=256)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b64"],
+    p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64"],
                    help="run one piece only (for profiling)")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()

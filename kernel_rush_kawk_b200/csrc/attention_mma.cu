@@ -419,10 +419,14 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, const float* __re
 }
 
 
-constexpr int FSTAGES = 2;  // page stages of the fused single-token kernel; three were measured: slower at batch 8 (fewer blocks fit an SM), no faster at 64
-constexpr size_t FUSED_BASE_BYTES =
-    ((size_t)FSTAGES * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)4 * 16 * (D + 2) * sizeof(float))
-        ? (size_t)FSTAGES * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)4 * 16 * (D + 2) * sizeof(float);
+// Page stages of the fused single-token kernel: two where the keys of a (sequence, kv head) are split over
+// a cluster (three blocks share an SM), three where one block walks them all (many sequences: two blocks
+// an SM, each with two pages in flight; at 64 sequences of 1,024 tokens 7 % faster than two stages and two
+// splits, while at 8 sequences three stages were slower).
+__host__ __device__ constexpr size_t fused_base_bytes(int stages) {
+  return ((size_t)stages * 2 * TILE_ELEMS * sizeof(bf16) > (size_t)4 * 16 * (D + 2) * sizeof(float))
+             ? (size_t)stages * 2 * TILE_ELEMS * sizeof(bf16) : (size_t)4 * 16 * (D + 2) * sizeof(float);
+}
 constexpr size_t PAGE_SMEM = (size_t)2 * 2 * TILE_ELEMS * sizeof(bf16);
 constexpr size_t RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
 constexpr size_t DECODE_SMEM = PAGE_SMEM > RED_SMEM ? PAGE_SMEM : RED_SMEM;
@@ -498,6 +502,7 @@ struct HeadRow {
   }
 };
 
+template <int FSTAGES>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
                               const void* __restrict__ q_gain, const void* __restrict__ k_gain, int gain_f32,
@@ -508,7 +513,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
                               int inbox_rows, int* __restrict__ error) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);                       // page buffers, later the partials
-  bf16* q_s = reinterpret_cast<bf16*>(smem_raw + FUSED_BASE_BYTES);          // [16][DP] rotated queries
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw + fused_base_bytes(FSTAGES));  // [16][DP] rotated queries
   bf16* kv_new = q_s + 16 * DP;                                         // [2][D] the new token's key and value
   float* inbox = reinterpret_cast<float*>(kv_new + 2 * D);              // [splits][inbox_rows][D + 2], used in block 0
   namespace cg = cooperative_groups;
@@ -730,8 +735,42 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   KRK_TRACE_END(2)
 }
 
-constexpr size_t FUSED_RED_SMEM = (size_t)4 * 16 * (D + 2) * sizeof(float);
-constexpr size_t FUSED_SMEM = FUSED_BASE_BYTES + (size_t)(16 * DP + 2 * D) * sizeof(bf16);
+template <int FSTAGES>
+int launch_decode_fused(bf16* out, const bf16* qkv, int q_stride, int HQ, int HKV, const void* q_gain, const void* k_gain,
+                        int gain_f32, const bf16* cos_t, const bf16* sin_t, float eps, const int* seq_slot,
+                        const int* seq_start, const int* table, int width, bf16* k_cache, bf16* v_cache, int n_seqs,
+                        float scale, int window, int splits, int n_pos, int* error, cudaStream_t stream) {
+  const int G = HQ / HKV;
+  const int row_tiles = (G + 15) / 16;
+  const int inbox_rows = G < 16 ? G : 16;
+  const size_t smem = fused_base_bytes(FSTAGES) + (size_t)(16 * DP + 2 * D) * sizeof(bf16) +
+                      (size_t)splits * inbox_rows * (D + 2) * sizeof(float);
+  if (smem > 220 * 1024) return -2;
+  auto kern = attention_decode_fused_kernel<FSTAGES>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, HKV * row_tiles, n_seqs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = splits;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, kern, out, qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, cos_t, sin_t, eps,
+                                 seq_slot, seq_start, table, width, k_cache, v_cache, scale * LOG2E, window, row_tiles,
+                                 n_pos, inbox_rows, error);
+}
 
 }  // namespace
 
@@ -809,35 +848,13 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
   const int row_tiles = (G + 15) / 16;
   if (HKV * row_tiles > 65535 || n_seqs > 65535) return -3;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -2;
-  const int inbox_rows = G < 16 ? G : 16;
-  const size_t smem = FUSED_SMEM + (size_t)splits * inbox_rows * (D + 2) * sizeof(float);
-  if (smem > 220 * 1024) return -2;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(splits, HKV * row_tiles, n_seqs);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = splits;
-  attr[1].val.clusterDim.y = 1;
-  attr[1].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_fused_kernel, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV,
-                                     q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot,
-                                     seq_start, table, width, (bf16*)k_cache, (bf16*)v_cache, scale * LOG2E, window,
-                                     row_tiles, n_pos, inbox_rows, error);
-  return (int)e;
+  if (splits == 1)
+    return launch_decode_fused<3>((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32,
+                                  (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot, seq_start, table, width,
+                                  (bf16*)k_cache, (bf16*)v_cache, n_seqs, scale, window, splits, n_pos, error, stream);
+  return launch_decode_fused<2>((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32,
+                                (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot, seq_start, table, width,
+                                (bf16*)k_cache, (bf16*)v_cache, n_seqs, scale, window, splits, n_pos, error, stream);
 }
 
 #endif  // head size served by the tensor-core kernels

@@ -417,10 +417,10 @@ class Kernels:
             out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
             row_tiles = -(-(heads // cache.kv_heads) // 16)
             # key splits (blocks per cluster) by the number of (sequence, kv head, row tile) items alone,
-            # never by lengths, so a captured step stays valid; measured best on B200 at 1, 8 and 64
-            # sequences of the 4B shape: 8, 4 and 2
+            # never by lengths, so a captured step stays valid; measured best on B200 at 1, 8, 16 and 32 or 64
+            # sequences of the 4B shape: 8, 4, 2 and 1 (one block per item runs a deeper page pipeline)
             items = n * cache.kv_heads * row_tiles
-            splits = 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 600 else 1
+            splits = 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 192 else 1
             gain = q_gain if q_gain is not None else k_gain
             n_pos = cos.shape[0] if cos is not None else 0x7fffffff
             self._ok(lib.krk_attention_decode_fused(
