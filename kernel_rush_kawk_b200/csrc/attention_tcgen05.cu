@@ -52,7 +52,7 @@ constexpr uint32_t TMEM_O = 256;       // O_t starts at column 256 + t * D; S_t 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;    // in log2 units: the reference maximum moves when outgrown by 2^8
 
-enum Bar { K_FULL = 0, V_FULL = 2, K_FREE = 4, V_FREE = 6, S_FULL = 8, P_READY = 10, O_DONE = 12, N_BARS = 14 };
+enum Bar { K_FULL = 0, V_FULL = 2, K_FREE = 4, V_FREE = 6, S_FULL = 8, P_READY = 10, O_DONE = 12, Q_FULL = 14, N_BARS = 15 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -80,7 +80,7 @@ __device__ __forceinline__ TileRange tile_range(int row_begin, int n_rows, int G
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                         bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
+                         const __grid_constant__ CUtensorMap map_q, int q_by_tma, bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
                          int width, float scale_log2, int window, int* __restrict__ error) {
@@ -104,35 +104,65 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const int start = seq_start[seq], slot = seq_slot[seq], row0 = cu_q[seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    tmem_slot[1] = (uint32_t)*reinterpret_cast<volatile int*>(error);  // a block that gave up: the others do no work
-  }
-  if (warp == 8) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  // the query tiles: row r, 16-byte piece c -> swizzled K-major sub-tiles; rows past the end are zero
-  for (int i = threadIdx.x; i < PAIR * (D / 8); i += THREADS) {
-    const int r = i / (D / 8), c = i % (D / 8);
-    const int R = pair * PAIR + r;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (R < n_rows) v = *reinterpret_cast<const uint4*>(qkv + (size_t)(row0 + R / G) * q_stride + (size_t)(kh * G + R % G) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + (r / ROWS) * TILE_BYTES + (c / 8) * SUB + swz(r % ROWS, c % 8)) = v;
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const bool dead = tmem_slot[1] != 0;
-
   const TileRange r0 = tile_range(pair * PAIR, n_rows, G, q_len, start, window);
   const TileRange r1 = tile_range(pair * PAIR + ROWS, n_rows, G, q_len, start, window);
   const int j_lo = r0.lo;                                   // tile 0 exists and starts no later than tile 1
   const int j_hi = r1.lo <= r1.hi ? max(r0.hi, r1.hi) : r0.hi;
   const int n = j_hi - j_lo + 1;
+
+  // TMA loads of the issuer (warp 8, lane 0); the first of them start before the block's first barrier
+  auto load_tile = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int i) {
+    mbar_expect_tx(bar, TILE_BYTES);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int page = table[(size_t)slot * width + (2 * (j_lo + i) + half) % width];
+      const int row = (page * HKV + kh) * KRK_PAGE;
+#pragma unroll
+      for (int h = 0; h < DB; ++h) tma_load_2d(dst + h * SUB + half * (64 * 128), map, bar, h * 64, row);
+    }
+  };
+  auto load_k = [&](int i) { load_tile(k_s + (i & 1) * TILE_BYTES, &map_k, bars + K_FULL + (i & 1), i); };
+  auto load_v = [&](int i) { load_tile(v_s + (i & 1) * TILE_BYTES, &map_v, bars + V_FULL + (i & 1), i); };
+
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      tmem_slot[1] = (uint32_t)*reinterpret_cast<volatile int*>(error);  // a block that gave up: the others do no work
+      if (q_by_tma) {
+        // a query tile is a box of 128 / G tokens x G heads x 64 dims per 64-wide block of the head: its rows
+        // land in (token, group member) order, which is the tile's row order
+        const int tiles_here = r1.lo <= r1.hi ? 2 : 1;
+        mbar_expect_tx(bars + Q_FULL, tiles_here * TILE_BYTES);
+        for (int t = 0; t < tiles_here; ++t)
+#pragma unroll
+          for (int h = 0; h < DB; ++h)
+            tma_load_3d(q_s + t * TILE_BYTES + h * SUB, &map_q, bars + Q_FULL, h * 64, kh * G, row0 + (pair * PAIR + t * ROWS) / G);
+      }
+      load_k(0);
+      load_v(0);
+      if (n > 1) load_k(1);
+    }
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (!q_by_tma) {
+    // the query tiles by hand: row r, 16-byte piece c -> swizzled K-major sub-tiles; rows past the end are zero
+    for (int i = threadIdx.x; i < PAIR * (D / 8); i += THREADS) {
+      const int r = i / (D / 8), c = i % (D / 8);
+      const int R = pair * PAIR + r;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (R < n_rows) v = *reinterpret_cast<const uint4*>(qkv + (size_t)(row0 + R / G) * q_stride + (size_t)(kh * G + R % G) * D + c * 8);
+      *reinterpret_cast<uint4*>(q_s + (r / ROWS) * TILE_BYTES + (c / 8) * SUB + swz(r % ROWS, c % 8)) = v;
+    }
+    fence_async_smem();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const bool dead = tmem_slot[1] != 0;
 
   if (dead) {
     // nothing to do
@@ -143,18 +173,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       bool ok = true;
       auto give_up = [&](int code) { atomicExch(error, code); ok = false; };
-      auto load_tile = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int i) {
-        mbar_expect_tx(bar, TILE_BYTES);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int page = table[(size_t)slot * width + (2 * (j_lo + i) + half) % width];
-          const int row = (page * HKV + kh) * KRK_PAGE;
-#pragma unroll
-          for (int h = 0; h < DB; ++h) tma_load_2d(dst + h * SUB + half * (64 * 128), map, bar, h * 64, row);
-        }
-      };
-      auto load_k = [&](int i) { load_tile(k_s + (i & 1) * TILE_BYTES, &map_k, bars + K_FULL + (i & 1), i); };
-      auto load_v = [&](int i) { load_tile(v_s + (i & 1) * TILE_BYTES, &map_v, bars + V_FULL + (i & 1), i); };
       auto qk = [&](int t, int i) {  // S_t = Q_t K_i^T
         const unsigned char* q = q_s + t * TILE_BYTES;
         const unsigned char* k = k_s + (i & 1) * TILE_BYTES;
@@ -174,10 +192,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                            idesc_o, (first && ks == 0) ? 0u : 1u);
       };
       const TileRange rng[2] = {r0, r1};
-      load_k(0);
-      load_v(0);
-      if (n > 1) load_k(1);
-      if (!mbar_wait(bars + K_FULL, 0)) give_up(6);
+      if (q_by_tma && !mbar_wait(bars + Q_FULL, 0)) give_up(14);
+      if (ok && !mbar_wait(bars + K_FULL, 0)) give_up(6);
       if (ok) {
         tc_fence_after();
         if (r0.has(j_lo)) qk(0, 0);
@@ -349,13 +365,13 @@ constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64;
 
 }  // namespace
 
-// Same arguments as krk_attention_prefill plus the cache's number of pages (for the TMA maps) and the
-// device error word. The keys and values of the step's own rows must be in the cache already.
+// Same arguments as krk_attention_prefill plus the cache's number of pages and the number of rows of qkv
+// (for the TMA maps) and the device error word. The keys and values of the step's own rows must be in the cache already.
 KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stride, int HQ, int HKV,
                                           const int* seq_slot, const int* seq_start, const int* seq_qlen,
                                           const int* cu_q, const int* table, int width, const void* k_cache,
-                                          const void* v_cache, int n_pages, int n_seqs, int max_q_len, float scale,
-                                          int window, int* error, cudaStream_t stream) {
+                                          const void* v_cache, int n_pages, int n_seqs, int max_q_len, int total_rows,
+                                          float scale, int window, int* error, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
   const int G = HQ / HKV;
   const long long tiles = ((long long)max_q_len * G + PAIR - 1) / PAIR;
@@ -367,6 +383,13 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
   if (rc) return rc;
   rc = make_map_bf16(&map_v, v_cache, rows, D, D, 64);
   if (rc) return rc;
+  // the query tiles come by TMA when a tile is a whole number of tokens (the group size divides 128)
+  const int q_by_tma = (ROWS % G == 0) ? 1 : 0;
+  CUtensorMap map_q = map_k;
+  if (q_by_tma) {
+    rc = make_map_bf16_3d(&map_q, qkv, D, HQ, total_rows, D, q_stride, G, ROWS / G);
+    if (rc) return rc;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
@@ -375,7 +398,7 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
   }
   dim3 grid((unsigned)(tiles * HKV), n_seqs, 1);
   attention_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
-      map_k, map_v, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
+      map_k, map_v, map_q, q_by_tma, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
       scale * LOG2E, window, error);
   KRK_CHECK_LAUNCH();
   return 0;

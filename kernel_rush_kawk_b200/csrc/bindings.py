@@ -54,7 +54,7 @@ _ATTN_SIGNATURES = {
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
-                                      c_float, c_int, _P, _P],
+                                      c_int, c_float, c_int, _P, _P],
     "krk_decode_layers_blocks": [c_int, c_int, c_int, c_int, c_int],
     "krk_decode_layers_partial_floats": [],
     "krk_decode_layers": [_P, _P],
@@ -456,7 +456,7 @@ class Kernels:
                 out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),
                 batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(), batch.cu_q.data_ptr(), cache.table.data_ptr(),
                 cache.width, cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], batch.n_seqs, batch.max_q_len,
-                scale, win, self.error.data_ptr(), self._stream()), "tcgen05 prefill attention")
+                rows, scale, win, self.error.data_ptr(), self._stream()), "tcgen05 prefill attention")
         elif fast and hasattr(lib, "krk_attention_prefill"):
             self._ok(lib.krk_attention_prefill(
                 out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),

@@ -52,6 +52,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
 // start address, stride between 8-row groups = 1024 bytes, descriptor version 1, swizzle mode 2.
 __device__ __forceinline__ uint64_t umma_desc(const void* smem_tile) {
@@ -164,6 +171,22 @@ inline int make_map_bf16(CUtensorMap* map, const void* base, long long rows, int
   cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -7;
+}
+
+// A bfloat16 tensor [n2][n1][n0] (n0 contiguous; strides in elements) read in boxes of box2 x box1 x 64 with
+// the 128-byte swizzle: in shared memory the box is box2 * box1 rows of 128 bytes, the middle index fastest.
+inline int make_map_bf16_3d(CUtensorMap* map, const void* base, long long n0, long long n1, long long n2, long long stride1,
+                            long long stride2, int box1, int box2) {
+  EncodeTiled fn = encode_fn();
+  if (!fn) return -6;
+  cuuint64_t dims[3] = {(cuuint64_t)n0, (cuuint64_t)n1, (cuuint64_t)n2};
+  cuuint64_t strides[2] = {(cuuint64_t)stride1 * 2, (cuuint64_t)stride2 * 2};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box1, (cuuint32_t)box2};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -7;
