@@ -60,6 +60,8 @@ class BatchMeta:
         self.buffer = torch.zeros(self.total, dtype=torch.int32, device=device)
         self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=self.buffer.is_cuda)
         self.host_np = self.host.numpy()
+        self._host_views = {name: self.host_np[off:off + size] for name, off, size in zip(self.FIELDS, offsets, sizes)}
+        self._single_token_shape = False  # the pinned buffer holds the constant arrays of a one-token-each pass
         for name, off, size in zip(self.FIELDS, offsets, sizes):
             setattr(self, name, self.buffer[off:off + size])
         self.copied = torch.cuda.Event() if self.buffer.is_cuda else None
@@ -73,25 +75,36 @@ class BatchMeta:
         self.q_lens: list[int] = []
 
     def host_field(self, name: str) -> np.ndarray:
-        i = self.FIELDS.index(name)
-        return self.host_np[self.offsets[i]:self.offsets[i] + self.sizes[i]]
+        return self._host_views[name]
 
     def fill(self, slots, starts, token_lists, want_rows) -> None:
         """Write one pass into the pinned buffer and start its copy to the device."""
         if self.copied is not None:
             self.copied.synchronize()  # the previous copy out of this pinned buffer is over
         q_lens = [len(t) for t in token_lists]
-        cu = np.zeros(len(q_lens) + 1, dtype=np.int32)
-        np.cumsum(q_lens, out=cu[1:])
-        self.host_field("tokens")[:] = np.concatenate([np.asarray(t, dtype=np.int32) for t in token_lists])
-        self.host_field("row_seq")[:] = np.repeat(np.arange(len(q_lens), dtype=np.int32), q_lens)
-        self.host_field("row_pos")[:] = np.concatenate(
-            [np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)])
-        self.host_field("seq_slot")[:] = slots
-        self.host_field("seq_start")[:] = starts
-        self.host_field("seq_qlen")[:] = q_lens
-        self.host_field("cu_q")[:] = cu
-        self.host_field("want")[:] = want_rows
+        view = self._host_views
+        if self.n_rows == self.n_seqs:
+            # one token each (this buffer's shape admits nothing else): row r is sequence r, and only the
+            # tokens, positions and slots change from step to step
+            if not self._single_token_shape:
+                n = self.n_seqs
+                view["row_seq"][:] = np.arange(n, dtype=np.int32)
+                view["seq_qlen"][:] = 1
+                view["cu_q"][:] = np.arange(n + 1, dtype=np.int32)
+                self._single_token_shape = True
+            view["tokens"][:] = [t[0] for t in token_lists]
+            view["row_pos"][:] = starts
+        else:
+            cu = np.zeros(len(q_lens) + 1, dtype=np.int32)
+            np.cumsum(q_lens, out=cu[1:])
+            view["tokens"][:] = np.concatenate([np.asarray(t, dtype=np.int32) for t in token_lists])
+            view["row_seq"][:] = np.repeat(np.arange(len(q_lens), dtype=np.int32), q_lens)
+            view["row_pos"][:] = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)])
+            view["seq_qlen"][:] = q_lens
+            view["cu_q"][:] = cu
+        view["seq_slot"][:] = slots
+        view["seq_start"][:] = starts
+        view["want"][:] = want_rows
         self.buffer.copy_(self.host, non_blocking=True)
         if self.copied is not None:
             self.copied.record()
