@@ -66,3 +66,46 @@ def test_four_b_layer_sizes_against_plain(big_folder, sequences, dtype):
         cache.free(s)
     cache.check()
     engine.ops.check()
+
+
+def test_fourteen_b_layer_sizes_against_plain(tmp_path):
+    """The Qwen3-14B layer sizes (hidden 5120, 40 query / 8 kv heads: groups of five, intermediate 17408,
+    untied head, theta 1e6) with one layer and a smaller vocabulary, in bfloat16: other tile counts and
+    a group size that does not divide the 128-row query tiles, whole and token by token in a batch."""
+    from kernel_rush_kawk_b200 import Engine, Qwen3Config, StepEntry, write_model_folder
+
+    base = Qwen3Config.preset("qwen3_14b").to_dict()
+    cfg14 = Qwen3Config.from_dict({**base, "num_hidden_layers": 1, "vocab_size": 32000})
+    scale = {f"model.layers.0.self_attn.{n}_norm.weight": 1.5 for n in ("q", "k")}
+    folder = write_model_folder(tmp_path / "m14", cfg14, 78, std=0.02, gain_std=0.05, scale=scale)
+    g = torch.Generator().manual_seed(6)
+    seqs = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (140, 35)]
+    cfg, w = plain.read_folder(folder)
+    refs = [plain.forward_logits(cfg, w, s, torch.float32, torch.bfloat16).float() for s in seqs]
+    engine = Engine(folder, dtype="bfloat16", max_tokens=1024, max_slots=4)
+    cache = engine.cache
+    slot = cache.alloc()
+    out = engine.step([StepEntry(slot, seqs[0], list(range(len(seqs[0]))))])
+    cache.free(slot)
+    assert_close(out, refs[0], "bfloat16", "14B sizes, whole")
+    cuts = [128, 30]
+    slots = [cache.alloc() for _ in seqs]
+    got = [[] for _ in seqs]
+    out = engine.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cuts)])
+    row = 0
+    for i, c in enumerate(cuts):
+        got[i].append(out[row:row + c].float().cpu())
+        row += c
+    fed = list(cuts)
+    while any(f < len(s) for f, s in zip(fed, seqs)):
+        live = [i for i in range(2) if fed[i] < len(seqs[i])]
+        out = engine.step([StepEntry(slots[i], [seqs[i][fed[i]]], [0]) for i in live]).float().cpu()
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1])
+            fed[i] += 1
+    for i, ref in enumerate(refs):
+        assert_close(torch.cat(got[i]), ref, "bfloat16", f"14B sizes, batch, request {i}")
+    for s in slots:
+        cache.free(s)
+    cache.check()
+    engine.ops.check()
