@@ -127,7 +127,10 @@ class Model:
         self.final_norm = self.tree.final_norm.part
         self.position = self.tree.position.part if self.tree.position is not None else None
         self.blocks = [block for block, _ in self.tree.layers]
-        self.graph_safe = all(getattr(block.mixer, "graph_safe", False) for block in self.blocks)
+        self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
+                              for part in (block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward))
+        if self.position is not None:
+            self.graph_safe = self.graph_safe and getattr(self.position, "graph_safe", False)
         self._decode_programs: dict = {}
 
     def cache_needs(self) -> list:

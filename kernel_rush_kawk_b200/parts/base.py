@@ -56,6 +56,10 @@ class StateNeed:
 class Part:
     """Base of every part."""
 
+    #: False if forward() reads data of the step on the host (lengths, a routing decision), so that a
+    #: single-token step with this part cannot be replayed from a captured graph
+    graph_safe = True
+
     def __init__(self, params: Mapping[str, Any]):
         self.params = dict(params)
 
@@ -85,10 +89,6 @@ class Norm(Part):
 
 
 class Mixer(Part):
-    #: False if forward() reads host-side batch data, so that a decode step with this
-    #: mixer cannot be replayed from a captured graph
-    graph_safe = True
-
     def cache_need(self):
         """KVNeed, StateNeed or None."""
         return None

@@ -1,7 +1,8 @@
 """Each part alone against the plain implementation, and the generality of the
 assembly: a toy mixer with state of its own, a layer that runs twice, a run that
-reads another run's cache -- registered, built and stepped from this file without
-a change to the package."""
+reads another run's cache; a feed-forward that routes rows to experts and a learned
+position table -- registered, built and stepped from this file without a change to
+the package."""
 
 import math
 from dataclasses import dataclass
@@ -318,3 +319,171 @@ def test_toy_architecture_with_a_state_mixer_a_repeated_layer_and_a_shared_cache
     engine.cache.check()
     toks = list(engine.generate([seqs[1]], 3))
     assert len(toks) == 3
+
+
+# ---------------------------------------------------------------------------------
+# A second toy architecture defined here: positions learned as a table added to the
+# embeddings (no rotation) and a feed-forward that routes every row to one of three
+# experts. Neither kind exists in the package.
+# ---------------------------------------------------------------------------------
+def register_routed_toy():
+    from kernel_rush_kawk_b200.config import ModelConfig, register_architecture
+    from kernel_rush_kawk_b200.parts import (FeedForward, LayerSpec, ModelPlan, PartSpec, PositionEncoding, ScheduleEntry,
+                                             TensorSpec, register_feed_forward, register_position)
+
+    class LearnedPositions(PositionEncoding):
+        """x_t += table[position of t]; queries and keys are not rotated."""
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.rows, self.hidden = int(params["table_rows"]), int(params["hidden"])
+
+        def tensor_specs(self):
+            return {"table": TensorSpec((self.rows, self.hidden))}
+
+        def bind(self, tensors, runtime):
+            self.table = tensors["table"]
+
+        def on_embeddings(self, ctx, x):
+            pos = ctx.batch.row_pos.long()  # a device array: nothing is read on the host
+            return (x.float() + self.table[pos].float()).to(x.dtype)
+
+    class RoutedSwiGLU(FeedForward):
+        """Router logits and their softmax in 32-bit; every row goes to its best expert (a SwiGLU of its own)
+        and comes back scaled by that expert's probability."""
+
+        graph_safe = False  # the rows of each expert are counted on the host
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.hidden, self.inter, self.experts = int(params["hidden"]), int(params["intermediate"]), int(params["experts"])
+
+        def tensor_specs(self):
+            specs = {"router": TensorSpec((self.experts, self.hidden))}
+            for e in range(self.experts):
+                specs[f"gate_up_{e}"] = TensorSpec((2 * self.inter, self.hidden))
+                specs[f"down_{e}"] = TensorSpec((self.hidden, self.inter))
+            return specs
+
+        def bind(self, tensors, runtime):
+            self.t = tensors
+
+        def forward(self, ctx, h):
+            rows = h.tensor()
+            logits = rows.float() @ self.t["router"].float().t()
+            prob, best = torch.softmax(logits, dim=-1).max(dim=-1)
+            out = torch.zeros_like(rows)
+            for e in range(self.experts):
+                idx = (best == e).nonzero().flatten()
+                if idx.numel() == 0:
+                    continue
+                part = rows.index_select(0, idx).contiguous()
+                act = ctx.ops.gate_up_swiglu(part, self.t[f"gate_up_{e}"], self.inter)
+                y = ctx.ops.linear(act, self.t[f"down_{e}"])
+                out.index_copy_(0, idx, (y.float() * prob[idx, None]).to(rows.dtype))
+            return out
+
+    register_position("test_learned_positions", LearnedPositions)
+    register_feed_forward("test_routed_swiglu", RoutedSwiGLU)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        hidden: int = 64
+        vocab: int = 113
+        architecture = "ToyRoutedForTests"
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw.get("hidden", 64), raw.get("vocab", 113))
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "hidden": self.hidden, "vocab": self.vocab}
+
+    def plan(cfg):
+        H = cfg.hidden
+        norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-6}, {"weight": name})
+        attn = lambda i: PartSpec(
+            "gqa_attention", {"hidden": H, "heads": 4, "kv_heads": 1, "head_dim": 32, "eps": 1e-6, "qk_norm": False},
+            {k: f"l{i}.attn.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        names = lambda i: {"router": f"l{i}.moe.router", **{f"gate_up_{e}": f"l{i}.moe.gate_up_{e}" for e in range(3)},
+                           **{f"down_{e}": f"l{i}.moe.down_{e}" for e in range(3)}}
+        routed = lambda i: PartSpec("test_routed_swiglu", {"hidden": H, "intermediate": 32, "experts": 3}, names(i))
+        layers = [LayerSpec("prenorm", norm(f"l{i}.n1"), attn(i), norm(f"l{i}.n2"), routed(i)) for i in range(2)]
+        return ModelPlan("ToyRoutedForTests", H, cfg.vocab,
+                         PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": H}, {"table": "embed"}),
+                         PartSpec("test_learned_positions", {"table_rows": 256, "hidden": H}, {"table": "positions"}),
+                         tuple(layers), (ScheduleEntry(0), ScheduleEntry(1)), norm("final"),
+                         PartSpec("output_head", {"vocab": cfg.vocab, "hidden": H}, {"weight": "head"}), 256)
+
+    register_architecture("ToyRoutedForTests", RoutedConfig, plan)
+    return RoutedConfig()
+
+
+def routed_plain(w, ids, rounding):
+    """The routed toy model, whole sequence; also returns every row's routing margin per layer."""
+    rt = (lambda t: t) if rounding is None else (lambda t: t.to(rounding).float())
+    T = len(ids)
+    x = rt(w["embed"][torch.tensor(ids)] + w["positions"][:T])
+    margins = []
+    for i in range(2):
+        h = plain.rms_norm(x, w[f"l{i}.n1"], 1e-6, rounding)
+        q = plain.linear(h, w[f"l{i}.attn.q_proj"], rounding).view(T, 4, 32)
+        k = plain.linear(h, w[f"l{i}.attn.k_proj"], rounding).view(T, 1, 32)
+        v = plain.linear(h, w[f"l{i}.attn.v_proj"], rounding).view(T, 1, 32)
+        a = plain.causal_gqa_attention(q, k, v, None, rounding)
+        x = plain.residual_add(x, plain.linear(a, w[f"l{i}.attn.o_proj"], rounding), rounding)
+        h = plain.rms_norm(x, w[f"l{i}.n2"], 1e-6, rounding)
+        logits = h @ w[f"l{i}.moe.router"].t()
+        prob = torch.softmax(logits, dim=-1)
+        top2 = logits.topk(2, dim=-1).values
+        margins.append(top2[:, 0] - top2[:, 1])
+        best = prob.argmax(dim=-1)
+        out = torch.zeros_like(h)
+        for e in range(3):
+            rows = best == e
+            gu = w[f"l{i}.moe.gate_up_{e}"]
+            y = plain.swiglu_mlp(h[rows], gu[:32], gu[32:], w[f"l{i}.moe.down_{e}"], rounding)
+            out[rows] = rt(y * prob[rows, e][:, None])
+        x = plain.residual_add(x, out, rounding)
+    return plain.rms_norm(x, w["final"], 1e-6, rounding) @ w["head"].t(), torch.stack(margins).min(dim=0).values
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_architecture_with_learned_positions_and_a_routed_feed_forward(dtype, tmp_path):
+    from kernel_rush_kawk_b200 import Engine, StepEntry, write_model_folder
+    from safetensors.torch import load_file
+
+    cfg = register_routed_toy()
+    scale = {f"l{i}.moe.router": 12.0 for i in range(2)}  # clear routing decisions
+    folder = write_model_folder(tmp_path / "routed", cfg, 9, std=0.08, gain_std=0.1, scale=scale)
+    engine = Engine(folder, dtype=NAME[dtype], max_tokens=1024, max_slots=4)
+    assert not engine.model.graph_safe and not engine.stepper.use_graphs
+    w = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    g = torch.Generator().manual_seed(4)
+    seqs = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (80, 12)]
+    rounding = None if dtype == torch.float32 else torch.bfloat16
+    refs, margins = zip(*[routed_plain(w, s, rounding) for s in seqs])
+    used = set()
+    for cuts in ([80, 12], [50, 2]):
+        slots = [engine.cache.alloc() for _ in seqs]
+        got = [[] for _ in seqs]
+        out = engine.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cuts)])
+        got[0].append(out[:cuts[0]]); got[1].append(out[cuts[0]:])
+        fed = list(cuts)
+        while any(f < len(s) for f, s in zip(fed, seqs)):
+            live = [i for i in range(2) if fed[i] < len(seqs[i])]
+            out = engine.step([StepEntry(slots[i], [seqs[i][fed[i]]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1]); fed[i] += 1
+        for i in range(2):
+            # a row whose two best experts are nearly tied may go either way once rounding differs:
+            # such rows, and the rows after them in the sequence, are left out
+            close_call = (margins[i] < (1e-3 if dtype == torch.float32 else 0.15)).nonzero().flatten()
+            keep = int(close_call[0]) if close_call.numel() else len(seqs[i])
+            used.add(keep)
+            assert_close(torch.cat(got[i])[:keep], refs[i][:keep], NAME[dtype], f"routed toy, cuts {cuts}, request {i}")
+        for s in slots:
+            engine.cache.free(s)
+    assert max(used) >= 12, "the routing margins left nothing to compare"
+    engine.cache.check()
+    assert len(list(engine.generate([seqs[1]], 3))) == 3
