@@ -54,14 +54,30 @@ def build_parser() -> argparse.ArgumentParser:
 
     from .replay import build_parser as replay_parser
     sub.add_parser("replay", parents=[replay_parser()], add_help=False, help="trace replay (see bin/trace_run)")
+    b = sub.add_parser("bench", help="the measurement script at the root of a source checkout (bench.py); "
+                                     "arguments after `bench` are passed to it")
     return p
 
 
 def main(argv=None) -> int:
-    args = build_parser().parse_args(argv)
+    parser = build_parser()
+    args, rest = parser.parse_known_args(argv)
+    if rest and args.command != "bench":
+        parser.error("unrecognized arguments: " + " ".join(rest))
     if args.command == "replay":
         from .replay import run
         return run(args)
+    if args.command == "bench":
+        import runpy
+        from pathlib import Path
+        script = Path(__file__).resolve().parent.parent / "bench.py"
+        if not script.is_file():
+            print(f"no bench.py beside the package ({script}): the measurement script ships with the source checkout",
+                  file=sys.stderr)
+            return 2
+        sys.argv = [str(script)] + list(rest)
+        runpy.run_path(str(script), run_name="__main__")
+        return 0
     if args.command == "write-random":
         from . import Qwen3Config, write_model_folder
         folder = write_model_folder(args.out, Qwen3Config.preset(args.preset), args.seed, args.std)

@@ -257,6 +257,34 @@ def test_rope_write_many_rows(ops, dtype, shape):
     assert torch.equal(qkv[:, heads * D:], qkv_ref[:, heads * D:]), "the step's own k and v columns stay as they were"
 
 
+@pytest.mark.parametrize("rows", [3, 300])
+def test_a_position_outside_the_rotary_table_is_flagged(ops, rows):
+    """A row whose position lies beyond the tables is reported through the error word and stores
+    nothing; the other rows are done as usual (both row kernels: few rows and many)."""
+    from kernel_rush_kawk_b200.csrc import KernelError
+
+    dtype, heads, kv_heads, D = torch.bfloat16, 4, 2, 32
+    width = 8
+    cache = make_cache(16, kv_heads, D, 1, width, dtype, 31)
+    before_k = cache.k.clone()
+    n_pos = rows + 5
+    inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(n_pos, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    batch = make_batch([0], [0], [rows])
+    batch.row_pos[1] = n_pos + 7  # one bad row
+    qkv = rand((rows, (heads + 2 * kv_heads) * D), dtype, 32)
+    raw = qkv.clone()
+    ops.qk_norm_rope_write(qkv, heads, kv_heads, D, None, None, 1e-6, cos, sin, batch, cache)
+    with pytest.raises(KernelError):
+        ops.check()
+    assert torch.equal(qkv[1], raw[1]), "the bad row is left as it was"
+    page, off = int(cache.table[0, 0]), 1
+    assert torch.equal(cache.k[page, :, off], before_k[page, :, off]), "and its key is not stored"
+    assert not torch.equal(qkv[2, :heads * D], raw[2, :heads * D]), "the rows around it are rotated"
+    ops.check()
+
+
 @pytest.mark.parametrize("shape", ATTN_SHAPES + [(40, 2, 64)])
 @pytest.mark.parametrize("window", [None, 70])
 @pytest.mark.parametrize("n_seqs", [1, 3, 40])
