@@ -66,7 +66,6 @@ class ClockSampler:
 
     def __init__(self):
         self.proc = None
-        self.path = ROOT / "gpurun_out"
 
     def start(self):
         try:

@@ -14,8 +14,8 @@ of the entries and of their ``want`` lists. After every step ``done <step>`` is
 printed and flushed. Nothing is sampled. The program drives the library's own
 engine: the model, step function, cache and kernels that generation uses.
 
-The reference's nearest things are its teacher-forced self-check and the judge's
-replay (engine/engine.py:522-560, QWEN_ENGINE_CONTRACT.md:105-123 of
+The reference's nearest things are its teacher-forced self-check and the replay its
+contract describes (engine/engine.py:522-560, QWEN_ENGINE_CONTRACT.md:105-123 of
 willzeng274/kernel-rush-kawk); it has no such program.
 """
 
