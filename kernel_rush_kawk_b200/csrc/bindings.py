@@ -204,10 +204,7 @@ class Kernels:
     """All kernels, for one device. ``head_dims``: the head sizes whose attention
     libraries are needed (compiled at first use)."""
 
-    # rows up to which the fused skinny kernels serve a bfloat16 product; the kernel takes up to 16, but from 9
-    # rows on (two 8-row tiles per weight fragment) the library product was measured faster: 2.82 against
-    # 3.08 ms a step at 16 sequences of the 4B shape
-    SKINNY_MAX_ROWS = 8
+    SKINNY_MAX_ROWS = 16  # rows up to which the fused skinny kernels serve a bfloat16 product
     # Every block of a skinny product redoes the norm of all rows in its prologue. That is
     # cheaper than a separate norm kernel for one or two rows and dearer beyond.
     FUSED_NORM_MAX_ROWS = 2

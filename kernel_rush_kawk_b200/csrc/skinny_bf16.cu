@@ -25,6 +25,13 @@ namespace {
 
 constexpr int CHUNK = 32;        // k values per fragment load
 constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 bytes each); DEEP doubles it
+// With two batch tiles whose rows ride in the ring (9 to 16 rows, no prologue) a stage is a third larger, and
+// at 8 loads an 8-warp block takes 131 KB of shared memory: one block per SM. Six keep two blocks per SM;
+// a decode step at 16 sequences of the 4B shape: 2.79 ms against 3.08 ms with 8 (and 2.96 / 3.06 / 3.30 ms
+// with 5 / 7 / 4; the library product: 2.83 ms).
+constexpr int RING_LOADS_TWO_TILES = 6;
+template <int NT, bool NORM, bool DEEP>
+__host__ __device__ constexpr int ring_loads() { return (NT == 2 && !NORM) ? RING_LOADS_TWO_TILES : (DEEP ? 2 : 1) * RING_LOADS; }
 
 // NT: 8-row batch tiles (1 or 2). RT: 16-row weight tiles per block; with SWIGLU the
 // block streams RT gate tiles and RT up tiles.
@@ -44,7 +51,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   KRK_TRACE_DECL
   constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;  // 16-row weight tiles this block streams
-  constexpr int STAGES = (DEEP ? 2 : 1) * RING_LOADS / TILES;
+  constexpr int STAGES = ring_loads<NT, NORM, DEEP>() / TILES;
   constexpr int XSLOTS = NORM ? 0 : NT;          // without the prologue the batch rows ride in the ring too
   constexpr int SLOTS = TILES * 2 + XSLOTS;      // 16-byte pieces per thread and stage
   constexpr size_t RING_BYTES = (size_t)STAGES * SLOTS * THREADS * 16;
@@ -261,7 +268,7 @@ int launch_warps(void* out, const void* x, const void* W, const void* branch, co
            int N, int K, float eps, cudaStream_t stream) {
   constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;
-  constexpr int STAGES = (DEEP ? 2 : 1) * RING_LOADS / TILES;
+  constexpr int STAGES = ring_loads<NT, NORM, DEEP>() / TILES;
   int pitch = 0;
   constexpr int SLOTS = TILES * 2 + (NORM ? 0 : NT);
   size_t smem = (size_t)STAGES * SLOTS * THREADS * 16 + (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);

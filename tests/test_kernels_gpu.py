@@ -117,19 +117,9 @@ def test_tcgen05_gemm_with_swiglu_epilogue(ops, mik):
 @pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
 @pytest.mark.parametrize("nk", [(96, 64), (160, 2560), (301, 96), (2560, 9728)])
 def test_fused_norm_linear_bfloat16(ops, rows, nk):
-    """The decode-time product with the residual add and the norm in its prologue. The kernel takes up to
-    16 rows; the library sends it up to 8 (beyond that the library product is faster), so the limit is
-    lifted here to keep the two-tile variants under test."""
+    """The decode-time product with the residual add and the norm in its prologue."""
     from kernel_rush_kawk_b200.parts.norm import Normed
 
-    ops.SKINNY_MAX_ROWS = 16
-    try:
-        _fused_norm_linear(ops, rows, nk, Normed)
-    finally:
-        del ops.SKINNY_MAX_ROWS
-
-
-def _fused_norm_linear(ops, rows, nk, Normed):
     n, k = nk
     dtype = torch.bfloat16
     ref = TorchOps(dtype)
@@ -153,14 +143,6 @@ def _fused_norm_linear(ops, rows, nk, Normed):
 def test_fused_gate_up_swiglu_bfloat16(ops, rows):
     from kernel_rush_kawk_b200.parts.norm import Normed
 
-    ops.SKINNY_MAX_ROWS = 16
-    try:
-        _fused_gate_up_swiglu(ops, rows, Normed)
-    finally:
-        del ops.SKINNY_MAX_ROWS
-
-
-def _fused_gate_up_swiglu(ops, rows, Normed):
     dtype, k, inter = torch.bfloat16, 160, 272
     ref = TorchOps(dtype)
     x, b = rand((rows, k), dtype, 14, 2.0), rand((rows, k), dtype, 15)
