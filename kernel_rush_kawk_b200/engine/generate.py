@@ -79,9 +79,17 @@ class GenerationLoop:
             live = list(seqs)
             entries = [StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live]
             step = 0
+            overlap = hasattr(self.sampler, "launch") and hasattr(self.stepper, "prepare_single_tokens")
             while live:
                 logits = self.stepper.step(entries)
-                tokens = self.sampler.select(logits, sampling, [s.request for s in live], step)
+                requests = [s.request for s in live]
+                if overlap and step + 1 < max_new_tokens:
+                    # while the device computes: the host's share of the next step, as if nobody stopped
+                    pending = self.sampler.launch(logits, sampling, requests, step)
+                    self.stepper.prepare_single_tokens([s.slot for s in live])
+                    tokens = self.sampler.finish(pending)
+                else:
+                    tokens = self.sampler.select(logits, sampling, requests, step)
                 self.steps += 1
                 out = [None] * len(seqs)
                 still = []

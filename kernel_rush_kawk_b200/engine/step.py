@@ -62,6 +62,7 @@ class BatchMeta:
         self.host_np = self.host.numpy()
         self._host_views = {name: self.host_np[off:off + size] for name, off, size in zip(self.FIELDS, offsets, sizes)}
         self._single_token_shape = False  # the pinned buffer holds the constant arrays of a one-token-each pass
+        self.places = None  # (slots, starts) that the pinned buffer was prepared for, tokens still to come
         for name, off, size in zip(self.FIELDS, offsets, sizes):
             setattr(self, name, self.buffer[off:off + size])
         self.copied = torch.cuda.Event() if self.buffer.is_cuda else None
@@ -77,10 +78,12 @@ class BatchMeta:
     def host_field(self, name: str) -> np.ndarray:
         return self._host_views[name]
 
-    def fill(self, slots, starts, token_lists, want_rows) -> None:
-        """Write one pass into the pinned buffer and start its copy to the device."""
+    def fill(self, slots, starts, token_lists, want_rows, upload: bool = True) -> None:
+        """Write one pass into the pinned buffer and start its copy to the device (``upload``
+        False: the copy waits for ``fill_tokens``)."""
         if self.copied is not None:
             self.copied.synchronize()  # the previous copy out of this pinned buffer is over
+        self.places = None
         q_lens = [len(t) for t in token_lists]
         view = self._host_views
         if self.n_rows == self.n_seqs:
@@ -105,14 +108,24 @@ class BatchMeta:
         view["seq_slot"][:] = slots
         view["seq_start"][:] = starts
         view["want"][:] = want_rows
-        self.buffer.copy_(self.host, non_blocking=True)
-        if self.copied is not None:
-            self.copied.record()
+        if upload:
+            self.upload()
         self.max_q_len = max(q_lens)
         self.max_kv_len = max(s + n for s, n in zip(starts, q_lens))
         self.is_decode = self.max_q_len == 1
         self.want_all = list(want_rows) == list(range(self.n_rows))
         self.slots, self.starts, self.q_lens = list(slots), list(starts), q_lens
+
+    def upload(self) -> None:
+        self.buffer.copy_(self.host, non_blocking=True)
+        if self.copied is not None:
+            self.copied.record()
+
+    def fill_tokens(self, token_lists) -> None:
+        """The tokens of a one-token-each pass whose places are in the pinned buffer already."""
+        self._host_views["tokens"][:] = [t[0] for t in token_lists]
+        self.places = None
+        self.upload()
 
     @property
     def bytes(self) -> int:
@@ -257,11 +270,31 @@ class Stepper:
         return None
 
     # -- decode from a captured graph ------------------------------------------
+    def prepare_single_tokens(self, slots) -> None:
+        """The host's share of the next step, if that step brings one token for each of ``slots``
+        (in this order): page reservation, page-table upload, positions and slots in the pinned
+        batch description. Everything here is independent of the tokens, so a caller does it while
+        the device still computes them. A step with other slots simply ignores the preparation."""
+        n = len(slots)
+        g = self._graphs.get(n) if self.use_graphs else None
+        if g is None:
+            return
+        cache = self.cache
+        starts = [cache.length[s] for s in slots]
+        for s, start in zip(slots, starts):
+            cache.reserve(s, start + 1)
+        cache.sync()
+        g.meta.fill(slots, starts, [[0]] * n, list(range(n)), upload=False)
+        g.meta.places = (list(slots), starts)
+
     def _replay(self, slots, starts, token_lists, want_rows, n: int):
         g = self._graphs.get(n)
         if g is None:
             g = self._capture(n, slots, starts, token_lists)
-        g.meta.fill(slots, starts, token_lists, list(range(n)))
+        if g.meta.places == (slots, starts):
+            g.meta.fill_tokens(token_lists)
+        else:
+            g.meta.fill(slots, starts, token_lists, list(range(n)))
         self.h2d_bytes += g.meta.bytes
         g.graph.replay()
         if len(want_rows) == n:

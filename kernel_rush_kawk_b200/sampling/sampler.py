@@ -45,6 +45,10 @@ class Sampler:
     def select(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], step: int) -> list[int]:
         """logits [n, vocab] float32; requests: each row's request index; step: how many
         tokens each of these requests has generated before this one."""
+        return self.finish(self.launch(logits, params, requests, step))
+
+    def launch(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], step: int):
+        """Start the selection and the copy of its result to the host; ``finish`` waits for it."""
         n = logits.shape[0]
         if self._requests_host != list(requests):
             self._requests_host = list(requests)
@@ -54,6 +58,9 @@ class Sampler:
             self._pinned = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=self.device.type == "cuda")
         host = self._pinned[:n]
         host.copy_(tokens, non_blocking=True)
+        return host
+
+    def finish(self, host) -> list[int]:
         if self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
         return host.tolist()
