@@ -6,12 +6,6 @@
 //   64 columns of S_t (two keys per 32-bit column) and is the A operand of O_t += P_t V.
 //   shared memory: Q0, Q1, and K and V double-buffered (128-byte swizzle, filled by TMA).
 //
-// The query rows may come as the QKV projection left them: each softmax thread then normalises and rotates
-// its row in shared memory before the first MMA (per-head RMSNorm and rotate-half RoPE with the rounding
-// points of rope_kv.cu), so rotated queries are never written to or read from global memory (33 MB a
-// layer at 2,048 tokens of the 4B shape; the step time did not change measurably: it is set by the
-// power-capped products).
-//
 // Warps 0..3 run the softmax of tile 0, warps 4..7 that of tile 1 (thread = query row = tensor-memory
 // lane); lane 0 of warp 8 issues every TMA load and every MMA, in the order
 //   ... PV0(j-1) QK0(j) PV1(j-1) QK1(j) PV0(j) QK0(j+1) ...
@@ -58,7 +52,7 @@ constexpr uint32_t TMEM_O = 256;       // O_t starts at column 256 + t * D; S_t 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;    // in log2 units: the reference maximum moves when outgrown by 2^8
 
-enum Bar { K_FULL = 0, V_FULL = 2, K_FREE = 4, V_FREE = 6, S_FULL = 8, P_READY = 10, O_DONE = 12, Q_FULL = 14, Q_READY = 15, N_BARS = 17 };
+enum Bar { K_FULL = 0, V_FULL = 2, K_FREE = 4, V_FREE = 6, S_FULL = 8, P_READY = 10, O_DONE = 12, Q_FULL = 14, N_BARS = 15 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -89,9 +83,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                          const __grid_constant__ CUtensorMap map_q, int q_by_tma, bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
-                         int width, float scale_log2, int window, int* __restrict__ error, int rope_q,
-                         const void* __restrict__ q_gain, int gain_f32, const bf16* __restrict__ cos_t,
-                         const bf16* __restrict__ sin_t, float eps, int n_pos) {
+                         int width, float scale_log2, int window, int* __restrict__ error) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = base;                    // two tiles
@@ -134,7 +126,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   if (warp == 8) {
     if (lane == 0) {
-      for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1 || i == Q_READY || i == Q_READY + 1) ? ROWS : 1);
+      for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       tmem_slot[1] = (uint32_t)*reinterpret_cast<volatile int*>(error);  // a block that gave up: the others do no work
       if (q_by_tma) {
@@ -200,12 +192,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                            idesc_o, (first && ks == 0) ? 0u : 1u);
       };
       const TileRange rng[2] = {r0, r1};
-      if (rope_q) {  // the softmax warps normalise and rotate the raw query rows in place first
-        if (!mbar_wait(bars + Q_READY, 0)) give_up(15);
-        if (ok && r1.lo <= r1.hi && !mbar_wait(bars + Q_READY + 1, 0)) give_up(15);
-      } else if (q_by_tma && !mbar_wait(bars + Q_FULL, 0)) {
-        give_up(14);
-      }
+      if (q_by_tma && !mbar_wait(bars + Q_FULL, 0)) give_up(14);
       if (ok && !mbar_wait(bars + K_FULL, 0)) give_up(6);
       if (ok) {
         tc_fence_after();
@@ -266,69 +253,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    if (rope_q && rng.lo <= rng.hi) {
-      // This row's query as the projection left it: per-head RMSNorm and rotation in place, with the rounding
-      // points of the stand-alone kernel (rope_kv.cu). The thread owns the whole row, so nothing is exchanged.
-      if (q_by_tma && !mbar_wait(bars + Q_FULL, 0)) { if (lane == 0) atomicExch(error, 14); ok = false; }
-      if (valid && ok) {
-        if (pos >= n_pos) {
-          atomicExch(error, 2);
-        } else {
-          constexpr int CH = D / 8, HALF = CH / 2;
-          unsigned char* tile_q = q_s + t * TILE_BYTES;
-          uint4 x[CH];
-          float sq = 0.f;
-#pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            x[c] = *reinterpret_cast<const uint4*>(tile_q + (c / 8) * SUB + swz(r, c % 8));
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x[c]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float lo2 = __low2float(xp[e]), hi2 = __high2float(xp[e]);
-              sq += lo2 * lo2 + hi2 * hi2;
-            }
-          }
-          if (q_gain) {
-            const float rstd = rsqrtf(sq / (float)D + eps);
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-              __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&x[c]);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 n2 = __floats2bfloat162_rn(__low2float(xp[e]) * rstd, __high2float(xp[e]) * rstd);
-                if (gain_f32) {
-                  const float* gp = reinterpret_cast<const float*>(q_gain) + c * 8 + 2 * e;
-                  xp[e] = __floats2bfloat162_rn(gp[0] * __low2float(n2), gp[1] * __high2float(n2));
-                } else {
-                  xp[e] = __hmul2_rn(reinterpret_cast<const __nv_bfloat162*>(q_gain)[c * 4 + e], n2);
-                }
-              }
-            }
-          }
-          if (cos_t) {
-#pragma unroll
-            for (int c = 0; c < HALF; ++c) {
-              const uint4 cv = *reinterpret_cast<const uint4*>(cos_t + (size_t)pos * (D / 2) + c * 8);
-              const uint4 sv = *reinterpret_cast<const uint4*>(sin_t + (size_t)pos * (D / 2) + c * 8);
-              __nv_bfloat162* y1 = reinterpret_cast<__nv_bfloat162*>(&x[c]);
-              __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&x[c + HALF]);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 cc = reinterpret_cast<const __nv_bfloat162*>(&cv)[e];
-                const __nv_bfloat162 ss = reinterpret_cast<const __nv_bfloat162*>(&sv)[e];
-                const __nv_bfloat162 a = y1[e], b = y2[e];
-                y1[e] = __hadd2_rn(__hmul2_rn(a, cc), __hmul2_rn(__hneg2(b), ss));
-                y2[e] = __hadd2_rn(__hmul2_rn(b, cc), __hmul2_rn(a, ss));
-              }
-            }
-          }
-#pragma unroll
-          for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(tile_q + (c / 8) * SUB + swz(r, c % 8)) = x[c];
-        }
-      }
-      fence_async_smem();
-      mbar_arrive(bars + Q_READY + t);
-    }
     for (int j = rng.lo; j <= rng.hi; ++j) {
       const uint32_t c = (uint32_t)(j - rng.lo);
       const int key0 = j * KEYS;
@@ -442,16 +366,12 @@ constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64;
 }  // namespace
 
 // Same arguments as krk_attention_prefill plus the cache's number of pages and the number of rows of qkv
-// (for the TMA maps) and the device error word. rope_q != 0: the query rows in qkv are as the projection
-// left them and the kernel normalises (q_gain, may be null) and rotates (cos_t / sin_t, may be null) them
-// itself, in shared memory; qkv is not written. The keys and values of the step's own rows must be in the cache already.
+// (for the TMA maps) and the device error word. The keys and values of the step's own rows must be in the cache already.
 KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stride, int HQ, int HKV,
                                           const int* seq_slot, const int* seq_start, const int* seq_qlen,
                                           const int* cu_q, const int* table, int width, const void* k_cache,
                                           const void* v_cache, int n_pages, int n_seqs, int max_q_len, int total_rows,
-                                          float scale, int window, int* error, int rope_q, const void* q_gain,
-                                          int gain_f32, const void* cos_t, const void* sin_t, float eps, int n_pos,
-                                          cudaStream_t stream) {
+                                          float scale, int window, int* error, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
   const int G = HQ / HKV;
   const long long tiles = ((long long)max_q_len * G + PAIR - 1) / PAIR;
@@ -479,7 +399,7 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
   dim3 grid((unsigned)(tiles * HKV), n_seqs, 1);
   attention_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
       map_k, map_v, map_q, q_by_tma, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
-      scale * LOG2E, window, error, rope_q, q_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, eps, n_pos);
+      scale * LOG2E, window, error);
   KRK_CHECK_LAUNCH();
   return 0;
 }

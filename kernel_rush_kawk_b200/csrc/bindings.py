@@ -40,7 +40,7 @@ _SIGNATURES = {
     "krk_gather_rows": [_P, _P, _P, c_int, c_int, c_int, _P, c_int, _P],
     "krk_swiglu": [_P, _P, c_int, c_int, c_int, _P],
     "krk_qk_norm_rope_write": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int,
-                               c_float, c_int, _P, c_int, c_int, _P],
+                               c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
     "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
@@ -54,7 +54,7 @@ _ATTN_SIGNATURES = {
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
-                                      c_int, c_float, c_int, _P, c_int, _P, c_int, _P, _P, c_float, c_int, _P],
+                                      c_int, c_float, c_int, _P, _P],
     "krk_decode_layers_blocks": [c_int, c_int, c_int, c_int, c_int],
     "krk_decode_layers_partial_floats": [],
     "krk_decode_layers": [_P, _P],
@@ -396,10 +396,7 @@ class Kernels:
         return self.swiglu(self.linear(h, w_gate_up), intermediate)
 
     # -- attention ------------------------------------------------------------------
-    def qk_norm_rope_write(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache,
-                           first_head=0):
-        """``first_head`` = ``heads`` leaves the query heads alone (for an attention kernel that normalises and
-        rotates them itself) and does the keys and values only."""
+    def qk_norm_rope_write(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache):
         gain = q_gain if q_gain is not None else k_gain
         n_pos = cos.shape[0] if cos is not None else 0x7fffffff
         self._ok(self.core.krk_qk_norm_rope_write(
@@ -407,7 +404,7 @@ class Kernels:
             _ptr(cos), _ptr(sin), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(),
             cache.table.data_ptr(), cache.width, cache.k.data_ptr() if kv_in_row else None,
             cache.v.data_ptr() if kv_in_row else None, qkv.shape[0], heads, kv_in_row, head_dim, eps, n_pos,
-            self.error.data_ptr(), _code(qkv.dtype), first_head, self._stream()), "q/k norm + rope + cache write")
+            self.error.data_ptr(), _code(qkv.dtype), self._stream()), "q/k norm + rope + cache write")
 
     def rope_attention(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache, scale,
                        window):
@@ -433,23 +430,10 @@ class Kernels:
                 cache.k.data_ptr(), cache.v.data_ptr(), n, scale, int(window or 0), splits, n_pos,
                 self.error.data_ptr(), self._stream()), "fused decode attention")
             return out
-        if self._takes_tcgen05_attention(qkv, heads, head_dim, batch, cache, lib):
-            # long steps: the attention kernel normalises and rotates the queries in shared memory, so the
-            # stand-alone kernel does the keys and values only and the rotated queries never travel
-            self.qk_norm_rope_write(qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache,
-                                    first_head=heads)
-            return self.attention(qkv, heads, kv_in_row, head_dim, batch, cache, scale, window,
-                                  rope_q=(q_gain, cos, sin, eps))
         self.qk_norm_rope_write(qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache)
         return self.attention(qkv, heads, kv_in_row, head_dim, batch, cache, scale, window)
 
-    def _takes_tcgen05_attention(self, qkv, heads, head_dim, batch, cache, lib) -> bool:
-        return (qkv.dtype == torch.bfloat16 and not batch.is_decode and self.use_tcgen05_attention
-                and head_dim in (64, 128) and hasattr(lib, "krk_attention_prefill_tcgen05") and qkv.shape[0] > 0
-                and batch.max_q_len * (heads // cache.kv_heads) >= 128 and qkv.stride(0) % 8 == 0)
-
-    def attention(self, qkv, heads, kv_in_row, head_dim, batch, cache, scale, window, rope_q=None):
-        """``rope_q`` = (q_gain, cos, sin, eps): the query rows are raw (tcgen05 kernel only)."""
+    def attention(self, qkv, heads, kv_in_row, head_dim, batch, cache, scale, window):
         lib = self._attn_lib(head_dim)
         rows = qkv.shape[0]
         out = torch.empty((rows, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
@@ -458,8 +442,6 @@ class Kernels:
         stride = qkv.stride(0)
         win = int(window or 0)
         fast = qkv.dtype == torch.bfloat16 and head_dim % 16 == 0
-        if rope_q is not None and not self._takes_tcgen05_attention(qkv, heads, head_dim, batch, cache, lib):
-            raise KernelError("raw query rows are taken by the tcgen05 attention kernel only")
         if fast and batch.is_decode and hasattr(lib, "krk_attention_decode"):
             splits, parts = self._decode_partials(batch.n_seqs, heads, cache.kv_heads, head_dim)
             self._ok(lib.krk_attention_decode(
@@ -467,16 +449,14 @@ class Kernels:
                 batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(),
                 cache.v.data_ptr(), batch.n_seqs, scale, win, splits, parts.data_ptr(), self._stream()),
                 "decode attention")
-        elif self._takes_tcgen05_attention(qkv, heads, head_dim, batch, cache, lib):
+        elif (fast and self.use_tcgen05_attention and head_dim in (64, 128) and hasattr(lib, "krk_attention_prefill_tcgen05")
+              and batch.max_q_len * (heads // cache.kv_heads) >= 128 and stride % 8 == 0):
             # long steps: the tcgen05 kernel (128-row tiles of (token, group member) pairs)
-            q_gain, cos, sin, eps = rope_q if rope_q is not None else (None, None, None, 0.0)
             self._ok(lib.krk_attention_prefill_tcgen05(
                 out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),
                 batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(), batch.cu_q.data_ptr(), cache.table.data_ptr(),
                 cache.width, cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], batch.n_seqs, batch.max_q_len,
-                rows, scale, win, self.error.data_ptr(), int(rope_q is not None), _ptr(q_gain),
-                int(q_gain is not None and q_gain.dtype == torch.float32), _ptr(cos), _ptr(sin), float(eps),
-                cos.shape[0] if cos is not None else 0x7fffffff, self._stream()), "tcgen05 prefill attention")
+                rows, scale, win, self.error.data_ptr(), self._stream()), "tcgen05 prefill attention")
         elif fast and hasattr(lib, "krk_attention_prefill"):
             self._ok(lib.krk_attention_prefill(
                 out.data_ptr(), qkv.data_ptr(), stride, heads, cache.kv_heads, batch.seq_slot.data_ptr(),

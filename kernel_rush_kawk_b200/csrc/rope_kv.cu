@@ -156,18 +156,17 @@ __global__ void qk_norm_rope_write_vec_kernel(bf16* __restrict__ qkv, const void
                                               const int* __restrict__ row_seq, const int* __restrict__ row_pos,
                                               const int* __restrict__ seq_slot, const int* __restrict__ table, int width,
                                               bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int rows, int HQ,
-                                              int HKV, int D, float eps, int n_pos, int* error, int first_head) {
+                                              int HKV, int D, float eps, int n_pos, int* error) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int lph = D / 8;  // lanes per head
   const int lane = threadIdx.x & 31;
   const int sub = lane % lph;  // this lane's 8 elements are [8 * sub, 8 * sub + 8)
   const int heads = HQ + 2 * HKV;
-  const int todo = heads - first_head;  // heads first_head.. of every row
   const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lph) + lane / lph;
-  const bool live = item < (long long)rows * todo;
-  const int row = live ? (int)(item / todo) : 0;
-  const int head = live ? first_head + (int)(item % todo) : first_head;
+  const bool live = item < (long long)rows * heads;
+  const int row = live ? (int)(item / heads) : 0;
+  const int head = live ? (int)(item % heads) : 0;
   const int raw_pos = row_pos[row];
   const bool bad = raw_pos < 0 || raw_pos >= n_pos;  // flagged below; nothing is stored for such a row
   const int pos = bad ? 0 : raw_pos;
@@ -200,7 +199,7 @@ qk_norm_rope_write_row_kernel(bf16* __restrict__ qkv, const void* __restrict__ q
                               const int* __restrict__ row_seq, const int* __restrict__ row_pos,
                               const int* __restrict__ seq_slot, const int* __restrict__ table, int width,
                               bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int HQ, int HKV, int D, float eps,
-                              int n_pos, int* error, int first_head) {
+                              int n_pos, int* error) {
   grid_launch_dependents();
   grid_dependency_wait();
   constexpr int U = 2;
@@ -221,7 +220,7 @@ qk_norm_rope_write_row_kernel(bf16* __restrict__ qkv, const void* __restrict__ q
   }
   RopeLane t;
   if (cos_t) t = rope_lane(cos_t, sin_t, pos, D, sub);
-  for (int base = first_head; base < heads; base += U * groups) {  // the same trip count for every lane
+  for (int base = 0; base < heads; base += U * groups) {  // the same trip count for every lane
     uint4 raw[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -253,34 +252,29 @@ qk_norm_rope_write_row_kernel(bf16* __restrict__ qkv, const void* __restrict__ q
 // from this many rows on, the block-per-row kernel; below it the flat one, whose few blocks start sooner
 constexpr int ROW_KERNEL_MIN_ROWS = 256;
 
-// first_head: 0, or HQ to leave the query heads as they are (a caller that rotates them itself) and do
-// the keys and values only.
 // gains may be null (no q/k norm); cos/sin may be null (no rotation); the cache
 // pointers are unused when HKV == 0.
 KRK_API int krk_qk_norm_rope_write(void* qkv, const void* q_gain, const void* k_gain, int gain_f32, const void* cos_t,
                                    const void* sin_t, const int* row_seq, const int* row_pos, const int* seq_slot,
                                    const int* table, int width, void* k_cache, void* v_cache, int rows, int HQ, int HKV,
-                                   int D, float eps, int n_pos, int* error, int dtype, int first_head,
-                                   cudaStream_t stream) {
+                                   int D, float eps, int n_pos, int* error, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
-  if (D % 2 || D > 4096 || first_head < 0 || first_head > HQ) return -2;
-  const long long items = (long long)rows * (HQ + 2 * HKV - first_head);
-  if (items == 0) return 0;
+  if (D % 2 || D > 4096) return -2;
+  const long long items = (long long)rows * (HQ + 2 * HKV);
   const bool gains_aligned = gain_f32 || ((((uintptr_t)q_gain) | ((uintptr_t)k_gain)) & 15) == 0;  // 16-byte gain loads
   if (dtype == KRK_DTYPE_BF16 && gains_aligned && (D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) {
     if (rows >= ROW_KERNEL_MIN_ROWS)
       return (int)launch_pdl(qk_norm_rope_write_row_kernel, dim3((unsigned)rows), dim3(256), 0, stream, (bf16*)qkv, q_gain,
                              k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, row_seq, row_pos, seq_slot, table,
-                             width, (bf16*)k_cache, (bf16*)v_cache, HQ, HKV, D, eps, n_pos, error, first_head);
+                             width, (bf16*)k_cache, (bf16*)v_cache, HQ, HKV, D, eps, n_pos, error);
     const int per_warp = 32 / (D / 8);
     const long long n_warps = (items + per_warp - 1) / per_warp;
     const long long n_blocks = (n_warps + 7) / 8;
     if (n_blocks > 0x7fffffffLL) return -3;
     return (int)launch_pdl(qk_norm_rope_write_vec_kernel, dim3((unsigned)n_blocks), dim3(256), 0, stream, (bf16*)qkv,
                            q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, row_seq, row_pos, seq_slot,
-                           table, width, (bf16*)k_cache, (bf16*)v_cache, rows, HQ, HKV, D, eps, n_pos, error, first_head);
+                           table, width, (bf16*)k_cache, (bf16*)v_cache, rows, HQ, HKV, D, eps, n_pos, error);
   }
-  if (first_head != 0) return -2;  // only the vector kernels skip heads
   const int warps = 8;
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -3;

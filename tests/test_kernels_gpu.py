@@ -353,43 +353,6 @@ def test_tcgen05_prefill_attention(ops, shape, window):
         close(got, other, dtype, "tcgen05 against mma.sync")
 
 
-@pytest.mark.parametrize("shape", [(8, 2, 64), (32, 8, 128), (10, 2, 128)])
-@pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("gains", [True, False])
-def test_rope_attention_of_long_steps(ops, shape, window, gains):
-    """Long bfloat16 steps at head sizes 64 and 128: the stand-alone kernel writes keys and values only and
-    the tcgen05 kernel normalises and rotates the raw query rows itself (groups of four: queries by TMA;
-    of five: by hand). Against the plain composition, prompts first, then pieces that continue them."""
-    heads, kv_heads, D = shape
-    dtype = torch.bfloat16
-    ref = TorchOps(dtype)
-    width, n_slots = 10, 3
-    cache = make_cache(34, kv_heads, D, n_slots, width, dtype, 95)
-    cache.window = window
-    ref_cache = SimpleNamespace(**vars(cache))
-    ref_cache.k, ref_cache.v = cache.k.clone(), cache.v.clone()
-    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
-    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
-    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
-    qg = (1.5 + 0.1 * rand((D,), torch.float32, 96)).to(dtype) if gains else None
-    kg = (0.8 + 0.1 * rand((D,), torch.float32, 97)).to(dtype) if gains else None
-    scale = 1.0 / math.sqrt(D)
-    steps = [([1, 2, 0], [0, 0, 0], [300, 129, 64]), ([2, 1], [129, 300], [200, 131])]
-    for s, (slots, starts, q_lens) in enumerate(steps):
-        batch = make_batch(slots, starts, q_lens)
-        qkv = rand((batch.n_rows, (heads + 2 * kv_heads) * D), dtype, 98 + s, 1.0)
-        raw = qkv.clone()
-        qkv_ref = qkv.clone()
-        got = ops.rope_attention(qkv, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, cache, scale, window)
-        ops.check()
-        want = ref.rope_attention(qkv_ref, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, ref_cache, scale, window)
-        assert torch.equal(qkv, raw), "the fused path leaves the projection's rows as they are"
-        close(cache.k, ref_cache.k, dtype, f"key pages, step {s}")
-        assert torch.equal(cache.v, ref_cache.v)
-        ref_cache.k.copy_(cache.k)
-        close(got, want, dtype, f"fused rope + tcgen05 attention, step {s} {shape} window {window} gains {gains}")
-
-
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("q_len", [1, 37])
 def test_one_far_key_among_hundreds_decides(ops, dtype, q_len):
