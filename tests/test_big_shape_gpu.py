@@ -109,3 +109,24 @@ def test_fourteen_b_layer_sizes_against_plain(tmp_path):
         cache.free(s)
     cache.check()
     engine.ops.check()
+
+
+def test_device_fed_steps_at_the_four_b_sizes(big_folder, sequences):
+    """The benchmark's way of stepping (tokens fed on the device, captured graph) against the generation
+    loop at the 4B layer sizes: the same greedy tokens."""
+    from kernel_rush_kawk_b200 import Engine, StepEntry
+
+    engine = Engine(big_folder, dtype="bfloat16", max_tokens=2048, max_slots=4)
+    prompts = [s[:n] for s, n in zip(sequences, (140, 40, 9))]
+    by_loop = list(engine.generate(prompts, 8))
+    cache = engine.cache
+    slots = [cache.alloc() for _ in prompts]
+    logits = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    first = logits.argmax(dim=-1).tolist()
+    assert first == by_loop[0]
+    rest = engine.stepper.decode_on_device(slots, first, 7, first_step=1).tolist()
+    assert rest == by_loop[1:]
+    for s in slots:
+        cache.free(s)
+    cache.check()
+    engine.ops.check()

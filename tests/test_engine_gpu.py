@@ -210,3 +210,30 @@ def test_persistent_decode_kernel(folders, name):
         for s, g, h in zip(seqs, *results):
             assert_close(g, plain_logits(folders[name], name, s, dtype), dtype, f"{name} persistent kernel, request of {len(s)}")
             assert torch.equal(g, h), "captured and eager steps of the persistent kernel must agree"
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_steps_fed_on_the_device_choose_the_same_tokens(folders, graphs, temperature):
+    """``decode_on_device`` runs single-token steps without a host round trip (the selection kernel writes
+    each step's tokens and positions into the next step's batch description). It must choose exactly the
+    tokens that the generation loop chooses with the host in between, for unequal prompts, greedily and
+    with temperature sampling, across a page boundary."""
+    from kernel_rush_kawk_b200 import StepEntry
+
+    name, dtype = "tiny_b", "bfloat16"
+    engine = engine_for(folders, name, dtype, graphs)
+    prompts = prompts_for(name, [60, 5, 33], seed=21)
+    new = 12
+    by_loop = list(engine.generate(prompts, new, temperature=temperature, seed=7))
+    cache = engine.cache
+    slots = [cache.alloc() for _ in prompts]
+    logits = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    first = engine.ops.select_tokens(logits, temperature, 7, torch.arange(3, dtype=torch.int32, device="cuda"), 0).tolist()
+    assert first == by_loop[0]
+    rest = engine.stepper.decode_on_device(slots, first, new - 1, temperature=temperature, seed=7, first_step=1).tolist()
+    assert rest == by_loop[1:], "device-fed steps must choose what the host-driven loop chooses"
+    for s in slots:
+        cache.free(s)
+    cache.check()
+    engine.ops.check()
