@@ -57,10 +57,13 @@ __device__ __forceinline__ void load_page(bf16* dst, const bf16* __restrict__ sr
 template <int NTILES>
 __device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&qf)[KSTEPS][4], const bf16* ks, int key0,
                                         int lane) {
+  // even and odd k-steps accumulate apart and are added at the end: two chains of KSTEPS / 2 dependent MMAs
+  // per n-tile instead of one of KSTEPS
+  float odd[NTILES][4];
 #pragma unroll
   for (int n = 0; n < NTILES; ++n)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+    for (int c = 0; c < 4; ++c) s[n][c] = odd[n][c] = 0.f;
 #pragma unroll
   for (int kk = 0; kk < KSTEPS; ++kk) {
 #pragma unroll
@@ -68,10 +71,19 @@ __device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&
       uint32_t b0, b1, b2, b3;
       const bf16* p = ks + kv_off(key0 + n * 8 + ((lane >> 4) << 3) + (lane & 7), kk * 2 + ((lane >> 3) & 1));
       ldmatrix_x4(b0, b1, b2, b3, p);
-      mma_bf16_16816(s[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
-      mma_bf16_16816(s[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+      if (kk & 1) {
+        mma_bf16_16816(odd[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+        mma_bf16_16816(odd[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+      } else {
+        mma_bf16_16816(s[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+        mma_bf16_16816(s[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+      }
     }
   }
+#pragma unroll
+  for (int n = 0; n < NTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s[n][c] += odd[n][c];
 }
 
 // O[16 x D] += P[16 x (8*NTILES)] . V for the same keys; p holds probabilities (float) in S's layout.
