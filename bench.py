@@ -19,9 +19,11 @@ at batch 1 and 64 (``points``); a 2,048-token prompt is prefilled (``prefill``).
   against the measured copy bandwidth.
 * ``prefill.frac``: the step's flops over its time over the measured bfloat16 peak.
 
-With --gpus above 1 it says that it runs on one GPU only and exits with 2. The
-reference cannot be installed offline (it has no setup.py or pyproject.toml), so
---impl reference prints its ``unavailable`` line.
+With --gpus above 1 it says that it runs on one GPU only and exits with 2.
+--impl reference runs the unmodified reference from baseline/_ref (a copy of its
+source tree: it is source-only, with no setup.py or pyproject.toml to install) on
+the same workload through its own entry point and prints the same line; where that
+copy, Triton or a CUDA device is missing it prints an ``unavailable`` line.
 """
 
 from __future__ import annotations
@@ -42,6 +44,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 PROMPT = 1024
 PREFILL_TOKENS = 2048
 SLOTS, CONTEXT = 64, 4096
+REPEATS = 5  # timed regions per decode point; the median is reported
 
 
 def peaks() -> dict:
@@ -250,6 +253,167 @@ def run_ours(args) -> dict:
     }
 
 
+def run_reference(args) -> dict:
+    """The unmodified reference (a copy of its tree under baseline/_ref) on the same workload, through
+    its own entry point: ``Engine(model_path).generate(input_ids, max_new_tokens)`` with equal-length
+    prompts (engine/engine.py:480,590 of willzeng274/kernel-rush-kawk). Its own switches turn off the
+    Transformers self-check and the token-recycling speculation (ENGINE_SELF_CHECK=0, ENGINE_RECYCLE=0,
+    engine.py:490,502), which leaves plain greedy decoding by graph replay (GraphPlan.run, :438-469):
+    the same work as this library's arm. Nothing of this package runs inside a timed region; it only
+    writes the random model folder that the reference then loads."""
+    import os
+    import tempfile
+
+    def unavailable(why: str) -> dict:
+        return {"impl": "reference", "unavailable": why}
+
+    ref_engine_dir = ROOT / "baseline" / "_ref" / "engine"
+    if not (ref_engine_dir / "engine.py").is_file():
+        return unavailable("no copy of the reference under baseline/_ref (it is source-only: a copy of its tree is its install)")
+    if args.gpus != 1:
+        return unavailable("the reference runs on one GPU only")
+    try:
+        import torch
+        import triton  # noqa: F401  (the reference's kernels)
+    except ImportError as exc:
+        return unavailable(f"import failed: {exc}")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    torch.cuda.set_device(0)
+
+    from kernel_rush_kawk_b200 import Qwen3Config, write_model_folder
+
+    base = Qwen3Config.preset("qwen3_4b")
+    full_layers = base.num_hidden_layers
+    layers = args.layers or full_layers
+    cfg = Qwen3Config.from_dict({**base.to_dict(), "num_hidden_layers": layers})
+    numbers = model_numbers(cfg, layers)
+    pk = peaks()
+    t0 = time.time()
+    os.environ["ENGINE_SELF_CHECK"] = "0"
+    os.environ["ENGINE_RECYCLE"] = "0"
+    gen = torch.Generator().manual_seed(1234)
+
+    def prompts(n, length):
+        return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
+
+    with tempfile.TemporaryDirectory(prefix="krk_ref_model_") as tmp:
+        folder = write_model_folder(Path(tmp) / "model", cfg, seed=0, std=0.02, device="cuda:0")
+        torch.cuda.empty_cache()
+        sys.path.insert(0, str(ref_engine_dir))
+        try:
+            import budget as ref_budget
+            import engine as ref_engine  # baseline/_ref/engine/engine.py
+            eng = ref_engine.Engine(str(folder))
+        except Exception as exc:  # noqa: BLE001
+            return unavailable(f"the reference failed to load: {exc!r}"[:300])
+    if eng.fallback is not None or eng.model is None:
+        return unavailable("the reference's own model failed to load here and it fell back to Transformers (see its log on stderr)")
+
+    def plan_for(batch, length, new):
+        ref_budget.start(ref_engine.PICKER_BUDGET_S)  # each shape gets the reference's whole tuning budget
+        plan = eng._plan(batch, length, new)
+        torch.cuda.synchronize()
+        return plan
+
+    def decode_point(batch: int):
+        """(device-timed tokens/s, ms per step, end-to-end tokens/s, ms per step, clocks)."""
+        total = args.warmup + args.steps
+        ids = prompts(batch, PROMPT)
+        for _ in eng.generate(ids, total):  # builds the plan, tunes, captures; one untimed sample
+            pass
+        if eng.fallback is not None:
+            raise RuntimeError("the reference gave up on its own engine and fell back to Transformers")
+        sampler = ClockSampler()
+        sampler.start()
+        it = eng.generate(ids, total)
+        for _ in range(args.warmup):
+            next(it)
+        torch.cuda.synchronize()
+        t_start = time.perf_counter()
+        n = 0
+        for _ in it:
+            n += 1
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t_start) * 1000.0 / max(n, 1)
+        # device-timed: the reference's captured decode step, replayed back to back
+        plan = eng.plans[(batch, PROMPT)]
+        plan.plan.ids.copy_(torch.tensor(ids, dtype=torch.int64))
+        plan._step_prefill()
+        for _ in range(args.warmup):
+            plan._step_decode()
+        times = []
+        for _ in range(REPEATS):
+            plan._step_prefill()
+            for _ in range(args.warmup):
+                plan._step_decode()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(args.steps):
+                plan._step_decode()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end) / args.steps)
+        clocks = sampler.stop()
+        ms = statistics.median(times)
+        return batch * 1000.0 / ms, ms, batch * 1000.0 / e2e_ms, e2e_ms, clocks
+
+    try:
+        value, ms_step, e2e_value, e2e_ms, clocks = decode_point(8)
+        mean_ctx = PROMPT + args.warmup + (args.steps + 1) / 2
+        step_bytes = numbers["weight_bytes"] + 8 * mean_ctx * numbers["kv_bytes_per_token"]
+        achieved = step_bytes / (ms_step * 1e-3) / 1e9
+        points, e2e_points, point_clocks = {}, {}, {}
+        for b in (1, 64):
+            v, ms_b, ev, _, ck = decode_point(b)
+            bytes_b = numbers["weight_bytes"] + b * mean_ctx * numbers["kv_bytes_per_token"]
+            points[f"decode_b{b}"] = round(v, 1)
+            points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            e2e_points[f"decode_b{b}"] = round(ev, 1)
+            point_clocks[f"decode_b{b}"] = ck
+        plan = plan_for(1, PREFILL_TOKENS, 1)
+        plan.plan.ids.copy_(torch.tensor(prompts(1, PREFILL_TOKENS), dtype=torch.int64))
+        sampler = ClockSampler()
+        sampler.start()
+        times = []
+        for i in range(args.warmup + 5):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            plan._step_prefill()
+            end.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(start.elapsed_time(end))
+        point_clocks["prefill"] = sampler.stop()
+    except Exception as exc:  # noqa: BLE001
+        return unavailable(f"the reference failed on this device: {exc!r}"[:300])
+    pre_ms = statistics.median(times)
+    T = PREFILL_TOKENS
+    flops = 2 * T * layers * numbers["per_layer"] + 2 * numbers["head"] + layers * 4 * numbers["attn_dim"] * T * (T + 1) / 2
+    prefill = {"value": round(T * 1000.0 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    return {
+        "metric": "decode tokens/s at batch 8 (Qwen3-4B shape, 1,024-token prompts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights normal(0, 0.02), seeded uniform token ids",
+        "config": {"model": "qwen3-4b-shape", "layers": layers, "layers_of_model": full_layers,
+                   "hidden": cfg.hidden_size, "intermediate": cfg.intermediate_size, "q_heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "vocab": cfg.vocab_size,
+                   "tied_head": cfg.tie_word_embeddings, "global_batch": 8, "prompt_len": PROMPT,
+                   "parallelism": "1 GPU", "switches": "ENGINE_SELF_CHECK=0 ENGINE_RECYCLE=0",
+                   "l2": "inputs larger than L2: a step reads %.1f GB" % (step_bytes / 1e9),
+                   "peaks": pk["source"], "hbm_peak_gbs": pk["hbm_gbs"], "bf16_peak_tflops": pk["bf16_tflops"]},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * 8, "points": e2e_points},
+        "gpu_launches": None, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "points": points, "clocks": clocks, "point_clocks": point_clocks, "impl": "reference",
+        "load_s": round(time.time() - t0, 1),
+    }
+
+
 def main() -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     p.add_argument("--gpus", type=int, default=1)
@@ -261,8 +425,8 @@ def main() -> int:
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference is not installable offline: pip finds neither "
-                          "setup.py nor pyproject.toml in it (it is a source-only Triton/H100 submission)"}))
+        args.warmup = max(args.warmup, 3)
+        print(json.dumps(run_reference(args)))
         return 0
     if args.gpus != 1:
         print(f"bench.py runs on one GPU only (this library has no multi-GPU path); got --gpus {args.gpus}")

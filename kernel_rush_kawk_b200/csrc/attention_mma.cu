@@ -937,58 +937,4 @@ extern "C" __attribute__((visibility("default"))) int krk_attention_decode_noall
   return 0;
 }
 
-// ---------------------------------------------------------------------------------
-// All layers of a single-token step as one persistent kernel (decode_layers.cuh).
-// ---------------------------------------------------------------------------------
-#include "decode_layers.cuh"
-
-// Blocks the kernel would run with for these sizes: one per SM, but never more than the row tiles of
-// the smallest projection (so that a row tile straddles at most two blocks). 0: sizes it does not take.
-KRK_API int krk_decode_layers_blocks(int M, int H, int HQ, int HKV, int I) {
-  if (M < 1 || M > 8 || HKV < 1 || HQ % HKV || HQ / HKV > 16) return 0;
-  if (H % 32 || I % 32 || (HQ * D) % 32 || H % 16 || I % 16 || ((HQ + 2 * HKV) * D) % 16) return 0;
-  int device = 0, sms = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return 0;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-  int blocks = sms;
-  blocks = min(blocks, (HQ + 2 * HKV) * D / 16);
-  blocks = min(blocks, H / 16);
-  blocks = min(blocks, I / 16);
-  return blocks;
-}
-
-// floats per work item of the attention partials, for the caller's scratch buffer
-KRK_API int krk_decode_layers_partial_floats() { return 16 * (D + 2); }
-
-// args: a decode_layers::Args in host memory (its pointers are device pointers). The barrier word, the
-// tile flags and the attention flags must be zero; the kernel leaves the flags zero, the barrier word
-// is cleared here. On return x1 holds the residual stream and branch the last projection's output,
-// still to be added.
-KRK_API int krk_decode_layers(const void* args_host, cudaStream_t stream) {
-  using namespace decode_layers;
-  Args a = *reinterpret_cast<const Args*>(args_host);
-  if (a.n_layers < 1) return -2;
-  const int blocks = krk_decode_layers_blocks(a.M, a.H, a.HQ, a.HKV, a.I);
-  if (blocks < 1 || a.splits < 1) return -2;
-  const int pad_bytes = (64 - (a.H * 2) % 128 + 128) % 128;
-  const int pitch = a.H + pad_bytes / 2;
-  const size_t att_bytes = (size_t)(2 * TILE_ELEMS + 16 * DP + 2 * D + 18 * D) * sizeof(bf16);
-  const size_t xs_bytes = max((size_t)a.M * pitch * sizeof(bf16), att_bytes);
-  const size_t smem = (size_t)RING * 2 * NTHREADS * 16 + (size_t)2 * WARPS * 2 * 128 * sizeof(float) + 64 + xs_bytes;
-  if (smem > 227 * 1024) return -2;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
-  cudaError_t e = cudaMemsetAsync(a.barrier, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) return (int)e;
-  int pitch_arg = pitch;
-  size_t xs_arg = xs_bytes;
-  void* params[] = {&a, &pitch_arg, &xs_arg};
-  e = cudaLaunchCooperativeKernel((const void*)decode_layers_kernel, dim3(blocks), dim3(NTHREADS), params, smem, stream);
-  if (e != cudaSuccess) return (int)e;
-  return 0;
-}
 #endif

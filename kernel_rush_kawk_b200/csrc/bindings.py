@@ -55,9 +55,6 @@ _ATTN_SIGNATURES = {
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
                                       c_int, c_float, c_int, _P, _P],
-    "krk_decode_layers_blocks": [c_int, c_int, c_int, c_int, c_int],
-    "krk_decode_layers_partial_floats": [],
-    "krk_decode_layers": [_P, _P],
     "krk_attention_decode_fused": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
                                    _P, c_int, c_float, c_int, c_int, c_int, _P, _P],
 }
@@ -77,127 +74,6 @@ def _load(path, signatures) -> ctypes.CDLL:
 
 def _ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
-
-
-class _DecodeLayer(ctypes.Structure):
-    """Mirror of decode_layers::Layer (csrc/decode_layers.cuh)."""
-    _fields_ = [(n, c_void_p) for n in ("w_qkv", "w_o", "w_gu", "w_down", "g_attn", "g_mlp", "g_q", "g_k", "k_cache",
-                                         "v_cache", "table")] + [
-        ("width", c_int), ("window", c_int), ("eps_attn", c_float), ("eps_mlp", c_float), ("eps_qk", c_float),
-        ("gains_f32", c_int)]
-
-
-class _DecodeArgs(ctypes.Structure):
-    """Mirror of decode_layers::Args."""
-    _fields_ = [("layers", c_void_p)] + [(n, c_int) for n in ("n_layers", "M", "H", "HQ", "HKV", "I")] + [
-        (n, c_void_p) for n in ("x0", "x1", "qkv", "attn", "branch", "act", "part", "tile_flags", "att_part",
-                                "att_flags", "barrier", "cos_t", "sin_t")] + [
-        ("n_pos", c_int), ("seq_slot", c_void_p), ("seq_start", c_void_p), ("scale_log2", c_float), ("splits", c_int),
-        ("error", c_void_p)]
-
-
-class DecodeProgram:
-    """All layers of a single-token step as one persistent kernel (csrc/decode_layers.cuh): the
-    layers' tensors as a table on the device, the scratch the kernel needs, and ``run``.
-
-    Built from the ``decode_fusion`` descriptions of a model's blocks, one per scheduled run, with
-    the cache view of each run. It takes steps of up to ``MAX_ROWS`` sequences in bfloat16 whose
-    layers are all pre-norm blocks of RMSNorm, grouped-query attention with a cache of their own,
-    and SwiGLU, with the same sizes throughout; ``build`` returns None for anything else."""
-
-    MAX_ROWS = 8
-    MAX_SPLITS = 16
-
-    @classmethod
-    def build(cls, kernels, fusions, views):
-        if not fusions or any(f is None or f.get("kind") != "prenorm" for f in fusions):
-            return None
-        first = fusions[0]
-        mix, ffn = first["mixer"], first["feed_forward"]
-        if (first["mixer_norm"].get("kind") != "rmsnorm" or mix.get("kind") != "gqa_attention"
-                or ffn.get("kind") != "swiglu"):
-            return None
-        H, HQ, HKV, D, I = mix["hidden"], mix["heads"], mix["kv_heads"], mix["head_dim"], ffn["intermediate"]
-        if D % 16 or D > 256:
-            return None
-        lib = kernels._attn_lib(D)
-        if not hasattr(lib, "krk_decode_layers") or lib.krk_decode_layers_blocks(1, H, HQ, HKV, I) < 1:
-            return None
-        rows = []
-        gains_f32 = None
-        for f, view in zip(fusions, views):
-            m, n1, n2, ff = f["mixer"], f["mixer_norm"], f["feed_forward_norm"], f["feed_forward"]
-            same = (n1.get("kind") == "rmsnorm" and n2.get("kind") == "rmsnorm" and m.get("kind") == "gqa_attention"
-                    and ff.get("kind") == "swiglu" and (m["hidden"], m["heads"], m["kv_heads"], m["head_dim"]) ==
-                    (H, HQ, HKV, D) and (ff["hidden"], ff["intermediate"]) == (H, I) and n1["size"] == H
-                    and n2["size"] == H and m["cos"] is mix["cos"] and m["scale"] == mix["scale"])
-            tensors = [m["w_qkv"], m["w_o"], ff["w_gate_up"], ff["w_down"], view.k, view.v]
-            gains = [n1["gain"], n2["gain"]] + [g for g in (m["q_gain"], m["k_gain"]) if g is not None]
-            if not same or any(t.dtype != torch.bfloat16 or not t.is_contiguous() for t in tensors):
-                return None
-            if (m["q_gain"] is None) != (m["k_gain"] is None) or len({g.dtype for g in gains}) != 1:
-                return None
-            if gains[0].dtype not in (torch.bfloat16, torch.float32) or any(g.data_ptr() % 16 for g in gains):
-                return None
-            f32 = int(gains[0].dtype == torch.float32)
-            if gains_f32 is None:
-                gains_f32 = f32
-            if f32 != gains_f32 or view.kv_heads != HKV or view.head_dim != D:
-                return None
-            rows.append(_DecodeLayer(
-                m["w_qkv"].data_ptr(), m["w_o"].data_ptr(), ff["w_gate_up"].data_ptr(), ff["w_down"].data_ptr(),
-                n1["gain"].data_ptr(), n2["gain"].data_ptr(), _ptr(m["q_gain"]), _ptr(m["k_gain"]), view.k.data_ptr(),
-                view.v.data_ptr(), view.table.data_ptr(), view.width, int(view.window or 0), n1["eps"], n2["eps"],
-                m["eps"], f32))
-        return cls(kernels, lib, rows, (H, HQ, HKV, D, I), mix["cos"], mix["sin"], mix["scale"],
-                   keep=[fusions, views])
-
-    def __init__(self, kernels, lib, rows, sizes, cos, sin, scale, keep):
-        self.kernels, self.lib, self.sizes = kernels, lib, sizes
-        self.cos, self.sin, self.scale = cos, sin, scale
-        self.keep = keep  # the tensors the table points to
-        H, HQ, HKV, D, I = sizes
-        dev = kernels.device
-        table = (_DecodeLayer * len(rows))(*rows)
-        raw = bytes(table)
-        self.n_layers = len(rows)
-        self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
-        tiles = max((HQ + 2 * HKV) * D, H, I) // 16
-        self.part = torch.zeros((2, tiles, 256), dtype=torch.float32, device=dev)
-        self.tile_flags = torch.zeros(tiles, dtype=torch.int32, device=dev)
-        self.att_flags = torch.zeros(self.MAX_ROWS * HKV, dtype=torch.int32, device=dev)
-        self.barrier = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.partial_floats = lib.krk_decode_layers_partial_floats()
-        self._att_part: dict = {}
-
-    def accepts(self, rows: int) -> bool:
-        H, HQ, HKV, D, I = self.sizes
-        return 1 <= rows <= self.MAX_ROWS and self.lib.krk_decode_layers_blocks(rows, H, HQ, HKV, I) >= 1
-
-    def run(self, x, batch):
-        """x [rows, hidden]: the embeddings (overwritten). Returns (x, branch): the residual
-        stream after the last layer and its last branch, still to be added."""
-        H, HQ, HKV, D, I = self.sizes
-        M = x.shape[0]
-        dev = x.device
-        blocks = self.lib.krk_decode_layers_blocks(M, H, HQ, HKV, I)
-        splits = max(1, min(self.MAX_SPLITS, blocks // (M * HKV)))
-        att_part = self._att_part.get((M, splits))
-        if att_part is None:
-            att_part = self._att_part[(M, splits)] = torch.empty(M * HKV * splits * self.partial_floats,
-                                                                 dtype=torch.float32, device=dev)
-        bf = dict(dtype=torch.bfloat16, device=dev)
-        x1, branch = torch.empty((M, H), **bf), torch.empty((M, H), **bf)
-        qkv, attn, act = torch.empty((M, (HQ + 2 * HKV) * D), **bf), torch.empty((M, HQ * D), **bf), torch.empty((M, I), **bf)
-        n_pos = self.cos.shape[0] if self.cos is not None else 0x7fffffff
-        args = _DecodeArgs(
-            self.table.data_ptr(), self.n_layers, M, H, HQ, HKV, I, x.data_ptr(), x1.data_ptr(), qkv.data_ptr(),
-            attn.data_ptr(), branch.data_ptr(), act.data_ptr(), self.part.data_ptr(), self.tile_flags.data_ptr(),
-            att_part.data_ptr(), self.att_flags.data_ptr(), self.barrier.data_ptr(), _ptr(self.cos), _ptr(self.sin),
-            n_pos, batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), self.scale * 1.4426950408889634, splits,
-            self.kernels.error.data_ptr())
-        self.kernels._ok(self.lib.krk_decode_layers(ctypes.byref(args), self.kernels._stream()), "decode layers")
-        return x1, branch
 
 
 class Kernels:
@@ -222,9 +98,6 @@ class Kernels:
         self._partials: dict = {}
         self._select_scratch = None
         self.use_tcgen05_attention = True
-        # whole single-token steps as one persistent kernel: measured slower than the layer-by-layer path
-        # (csrc/decode_layers.cuh has the figures), so only on request
-        self.use_decode_program = os.environ.get("KRK_DECODE_PROGRAM") == "1"
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -262,13 +135,6 @@ class Kernels:
 
     def empty_like(self, x):
         return torch.empty_like(x)
-
-    def decode_program(self, fusions, views):
-        """A DecodeProgram for these scheduled runs (their blocks' ``decode_fusion`` dicts and
-        cache views), or None if the persistent kernel does not take them."""
-        if not self.use_decode_program:
-            return None
-        return DecodeProgram.build(self, fusions, views)
 
     @staticmethod
     def _resolve(x):

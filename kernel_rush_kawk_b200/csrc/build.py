@@ -28,7 +28,7 @@ SRC_DIR = Path(__file__).parent
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu"]
 ATTN_SOURCES = ["attention_simple.cu", "attention_mma.cu", "attention_tcgen05.cu"]
-HEADERS = ["common.cuh", "mma.cuh", "tcgen05.cuh", "attention_noalloc.h", "decode_layers.cuh"]
+HEADERS = ["common.cuh", "mma.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

@@ -131,24 +131,9 @@ class Model:
                               for part in (block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward))
         if self.position is not None:
             self.graph_safe = self.graph_safe and getattr(self.position, "graph_safe", False)
-        self._decode_programs: dict = {}
 
     def cache_needs(self) -> list:
         return self.tree.cache_needs()
-
-    def _decode_program(self, ctx):
-        """The kernels' program for whole single-token steps over this cache, if they offer one
-        for this model's blocks (built once per cache)."""
-        key = id(ctx.cache)
-        if key not in self._decode_programs:
-            program = None
-            build = getattr(ctx.ops, "decode_program", None)
-            if build is not None and all(e.cache_from is None for e in self.plan.schedule):
-                fusions = [self.blocks[e.layer].decode_fusion() for e in self.plan.schedule]
-                if all(f is not None for f in fusions):
-                    program = build(fusions, [ctx.cache_view(run) for run in range(len(fusions))])
-            self._decode_programs[key] = (program, ctx.cache)  # the cache is kept alive with its key
-        return self._decode_programs[key][0]
 
     def forward(self, ctx, want_rows) -> torch.Tensor:
         """Run the schedule over ctx.batch's rows; return float32 logits
@@ -159,12 +144,8 @@ class Model:
         if self.position is not None:
             x = self.position.on_embeddings(ctx, x)
         stream = Stream(x)
-        program = self._decode_program(ctx) if getattr(ctx.batch, "is_decode", False) else None
-        if program is not None and x.dtype == torch.bfloat16 and program.accepts(x.shape[0]):
-            stream.x, stream.branch = program.run(x, ctx.batch)
-        else:
-            for run, entry in enumerate(self.plan.schedule):
-                stream = self.blocks[entry.layer].forward(ctx, stream, ctx.cache_view(run))
+        for run, entry in enumerate(self.plan.schedule):
+            stream = self.blocks[entry.layer].forward(ctx, stream, ctx.cache_view(run))
         if want_rows is not None and not getattr(ctx.batch, "want_all", False):  # all rows in order: nothing to gather
             stream.x = ops.gather_rows(stream.x, want_rows)
             if stream.branch is not None:

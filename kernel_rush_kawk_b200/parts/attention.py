@@ -77,16 +77,6 @@ class GQAttention(Mixer):
         self.q_gain = tensors.get("q_norm")
         self.k_gain = tensors.get("k_norm")
 
-    def decode_fusion(self):
-        if not self.own_cache:
-            return None
-        tables = self.position.rotary_tables() if self.position is not None else None
-        cos, sin = tables if tables is not None else (None, None)
-        return {"kind": "gqa_attention", "w_qkv": self.w_qkv, "w_o": self.w_o, "q_gain": self.q_gain,
-                "k_gain": self.k_gain, "eps": self.eps, "hidden": self.hidden, "heads": self.heads,
-                "kv_heads": self.kv_heads, "head_dim": self.head_dim, "window": self.window, "scale": self.scale,
-                "cos": cos, "sin": sin}
-
     # -- compute ----------------------------------------------------------
     def forward(self, ctx, h, cache):
         ops = ctx.ops

@@ -74,12 +74,6 @@ class Part:
         """Nothing to do by default; parts that fuse tensors keep the originals' names
         only in the plan, never on disk."""
 
-    def decode_fusion(self):
-        """What a kernel that runs whole layers of a single-token step needs to know of
-        this part: a dict with a ``kind`` and the part's tensors and constants, or None
-        (the default) if the part only runs through ``forward``."""
-        return None
-
 
 class Norm(Part):
     def forward(self, ctx, stream: "Stream"):
@@ -129,10 +123,6 @@ class Block:
 
     def forward(self, ctx, stream: "Stream", cache) -> "Stream":
         raise NotImplementedError
-
-    def decode_fusion(self):
-        """The arrangement's kind with its four parts' ``decode_fusion`` dicts, or None."""
-        return None
 
 
 class Stream:

@@ -24,13 +24,5 @@ class PreNormBlock(Block):
         stream.branch = branch
         return stream
 
-    def decode_fusion(self):
-        parts = [self.mixer_norm.decode_fusion(), self.mixer.decode_fusion(), self.feed_forward_norm.decode_fusion(),
-                 self.feed_forward.decode_fusion()]
-        if any(p is None for p in parts):
-            return None
-        return {"kind": "prenorm", "mixer_norm": parts[0], "mixer": parts[1], "feed_forward_norm": parts[2],
-                "feed_forward": parts[3]}
-
 
 register_block("prenorm", PreNormBlock)

@@ -33,10 +33,6 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([tensors["gate_proj"], tensors["up_proj"]], dim=0).contiguous()
         self.w_down = tensors["down_proj"].contiguous()
 
-    def decode_fusion(self):
-        return {"kind": "swiglu", "w_gate_up": self.w_gate_up, "w_down": self.w_down, "hidden": self.hidden,
-                "intermediate": self.intermediate}
-
     def forward(self, ctx, h):
         act = ctx.ops.gate_up_swiglu(h, self.w_gate_up, self.intermediate)
         return ctx.ops.linear(act, self.w_down)

@@ -68,9 +68,6 @@ class RMSNorm(Norm):
         self.gain = tensors["weight"]
         self.ops = runtime.ops
 
-    def decode_fusion(self):
-        return {"kind": "rmsnorm", "gain": self.gain, "eps": self.eps, "size": self.size}
-
     def forward(self, ctx, stream: Stream) -> Normed:
         if stream.branch is None:
             return Normed(self.ops, stream.x, None, self.gain, self.eps, stream.x)

@@ -186,32 +186,6 @@ def test_stop_tokens_end_a_sequence_early(folders):
     assert engine.cache.live == 0
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
-def test_persistent_decode_kernel(folders, name):
-    """Single-token steps of up to eight sequences as one persistent kernel over all layers (off by
-    default): the last 32 tokens one by one, unequal batches whose shorter requests end earlier, a
-    second batch on reused slots, with and without graph capture."""
-    from kernel_rush_kawk_b200 import Engine
-
-    dtype = "bfloat16"
-    engines = []
-    for graphs in (True, False):
-        engine = Engine(folders[name], dtype=dtype, max_tokens=8192, max_slots=8, use_cuda_graphs=graphs)
-        engine.ops.use_decode_program = True
-        engines.append(engine)
-    engine = engines[0]
-    seq = prompts_for(name, [130], seed=12)[0]
-    got = run_schedule(engine, [seq], [len(seq) - 32])[0]
-    assert any(p is not None for p, _ in engine.model._decode_programs.values()), "the persistent kernel was not used"
-    assert_close(got, plain_logits(folders[name], name, seq, dtype), dtype, f"{name} last 32, persistent kernel")
-    for seed, lengths, prompt_lens in ((13, [40, 9, 101, 70, 33], [5, 8, 66, 64, 1]), (14, [77, 140, 12], [70, 1, 11])):
-        seqs = prompts_for(name, lengths, seed=seed)
-        results = [run_schedule(e, seqs, prompt_lens) for e in engines]
-        for s, g, h in zip(seqs, *results):
-            assert_close(g, plain_logits(folders[name], name, s, dtype), dtype, f"{name} persistent kernel, request of {len(s)}")
-            assert torch.equal(g, h), "captured and eager steps of the persistent kernel must agree"
-
-
 @pytest.mark.parametrize("graphs", [True, False])
 @pytest.mark.parametrize("temperature", [0.0, 0.9])
 def test_steps_fed_on_the_device_choose_the_same_tokens(folders, graphs, temperature):
