@@ -166,6 +166,14 @@ class SequenceCache:
             g.table.index_copy_(0, idx, torch.from_numpy(g.table_host[rows]).to(self.device))
             g.dirty.clear()
 
+    def per_sequence_step_limit(self) -> int | None:
+        """The most tokens one sequence may bring in one pass, or None if any number will do. A group that
+        keeps a window of keys cycles through a ring of pages sized for ``step_tokens`` new positions;
+        a longer pass would overwrite keys that its own first rows still have to read."""
+        if any(g.need.window is not None for g in self._kv_groups):
+            return self.step_tokens
+        return None
+
     # -- views --------------------------------------------------------------
     def view(self, run: int):
         where = self._where[run]

@@ -79,8 +79,9 @@ def main(argv=None) -> int:
         runpy.run_path(str(script), run_name="__main__")
         return 0
     if args.command == "write-random":
-        from . import Qwen3Config, write_model_folder
-        folder = write_model_folder(args.out, Qwen3Config.preset(args.preset), args.seed, args.std)
+        from . import write_model_folder
+        from .config.registry import preset_config
+        folder = write_model_folder(args.out, preset_config(args.preset), args.seed, args.std)
         print(folder)
         return 0
     from . import Engine

@@ -31,6 +31,15 @@ class ModelConfig:
         raise NotImplementedError
 
     @classmethod
+    def preset_names(cls) -> list[str]:
+        """Names of the configurations this class keeps ready (none by default)."""
+        return []
+
+    @classmethod
+    def preset(cls, name: str) -> "ModelConfig":
+        raise ConfigError(f"unknown preset '{name}'; known presets: {cls.preset_names()}")
+
+    @classmethod
     def from_json(cls, path) -> "ModelConfig":
         path = Path(path)
         if path.is_dir():

@@ -151,12 +151,15 @@ class Qwen3Config(ModelConfig):
         return d
 
     @classmethod
+    def preset_names(cls) -> list[str]:
+        return sorted(p.stem for p in PRESET_DIR.glob("*.json"))
+
+    @classmethod
     def preset(cls, name: str) -> "Qwen3Config":
         """A named configuration kept as a JSON file beside this module."""
         path = PRESET_DIR / f"{name}.json"
         if not path.is_file():
-            known = sorted(p.stem for p in PRESET_DIR.glob("*.json"))
-            raise ConfigError(f"unknown preset '{name}'; known presets: {known}")
+            raise ConfigError(f"unknown preset '{name}'; known presets: {cls.preset_names()}")
         return cls.from_dict(json.loads(path.read_text()))
 
     def window_of(self, layer: int) -> int | None:

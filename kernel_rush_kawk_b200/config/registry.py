@@ -70,6 +70,18 @@ def read_config(folder_or_dict) -> tuple[Architecture, ModelConfig]:
     return arch, arch.config_class.from_dict(raw)
 
 
+def preset_config(name: str) -> ModelConfig:
+    """The named ready-made configuration of whichever registered architecture keeps one of that name."""
+    _load_builtin()
+    known = {}
+    for arch in _REGISTRY.values():
+        names = arch.config_class.preset_names()
+        if name in names:
+            return arch.config_class.preset(name)
+        known[arch.name] = names
+    raise ConfigError(f"unknown preset '{name}'; known presets by architecture: {known}")
+
+
 _builtin_loaded = False
 
 

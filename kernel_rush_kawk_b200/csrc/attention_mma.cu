@@ -877,6 +877,8 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
 // the limits, and the rules on first call and on overlapping calls).
 // ---------------------------------------------------------------------------------
 #if KRK_HEAD_DIM % 16 == 0 && KRK_HEAD_DIM <= 256
+#include <mutex>
+
 #include "attention_noalloc.h"
 
 static __device__ __align__(256) float krk_noalloc_scratch[KRK_NOALLOC_SCRATCH_BYTES / sizeof(float)];
@@ -886,12 +888,15 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 // Device address of the array per device. In host code the array's name is only a
 // handle for the runtime, not an address a kernel could use.
 float* noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex noalloc_setup_lock;
 }  // namespace
 
 extern "C" __attribute__((visibility("default"))) const char* krk_attention_decode_noalloc_strerror(int code) {
   switch (code) {
     case 0: return "ok";
     case -3: return "the grid would be too large (too many kv heads or sequences), or splits < 1";
+    case KRK_NOALLOC_BAD_SHAPE:
+      return "HQ and HKV must be positive with HQ a multiple of HKV, width positive, and q_stride at least (HQ + 2 HKV) * head_dim";
     case KRK_NOALLOC_TOO_LARGE:
       return "n_seqs * HQ * splits * (head_dim + 2) floats exceed the library's fixed 4 MiB scratch; "
              "use fewer splits or sequences per call, or krk_attention_decode with a scratch buffer of your own";
@@ -905,6 +910,7 @@ extern "C" __attribute__((visibility("default"))) int krk_attention_decode_noall
     const int* table, int width, const void* k_cache, const void* v_cache, int n_seqs, float scale, int window,
     int splits, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
+  if (n_seqs < 0 || HKV < 1 || HQ < 1 || HQ % HKV != 0 || width < 1 || q_stride < (HQ + 2 * HKV) * D) return KRK_NOALLOC_BAD_SHAPE;
   const int G = HQ / HKV;
   const int row_tiles = (G + 15) / 16;
   if (HKV * row_tiles > 65535 || n_seqs > 65535 || splits < 1) return -3;
@@ -915,6 +921,7 @@ extern "C" __attribute__((visibility("default"))) int krk_attention_decode_noall
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess) return (int)err;
   if (device < 0 || device >= NOALLOC_MAX_DEVICES) return KRK_NOALLOC_SETUP_FAILED;
+  std::lock_guard<std::mutex> guard(noalloc_setup_lock);  // host threads may call at the same time
   if (noalloc_scratch_ptr[device] == nullptr) {  // once per device, with that device current
     float* p = nullptr;
     err = cudaGetSymbolAddress((void**)&p, krk_noalloc_scratch);

@@ -19,6 +19,9 @@
 //  * The first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress) and sets the kernel's shared-memory attribute. Make that
 //    first call outside any stream capture.
+//  * Head counts and strides are checked before anything else (KRK_NOALLOC_BAD_SHAPE);
+//    host threads may call concurrently (the per-device set-up is serialised), but
+//    see the next point for what their kernels may not do.
 //  * All calls share the one array and it keeps the last call's contents. Nothing
 //    in it has to start at zero: every (sequence, head, split) partial is written
 //    before the merge reads it. Two calls that overlap on the GPU (different
@@ -35,6 +38,7 @@
 #define KRK_NOALLOC_SCRATCH_BYTES (4u << 20)
 #define KRK_NOALLOC_TOO_LARGE (-5)
 #define KRK_NOALLOC_SETUP_FAILED (-6)
+#define KRK_NOALLOC_BAD_SHAPE (-7)
 
 #ifdef __cplusplus
 extern "C" {

@@ -128,7 +128,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     if (lane == 0) {
       for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      tmem_slot[1] = (uint32_t)*reinterpret_cast<volatile int*>(error);  // a block that gave up: the others do no work
+      // a block of this step that gave up on a wait (codes from 3 on): the others do no work. The host reads and
+      // clears the word at the end of every step, so a flag never outlives the step that raised it.
+      tmem_slot[1] = (uint32_t)(*reinterpret_cast<volatile int*>(error) >= 3);
       if (q_by_tma) {
         // a query tile is a box of 128 / G tokens x G heads x 64 dims per 64-wide block of the head: its rows
         // land in (token, group member) order, which is the tile's row order

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
     "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "krk_selftest_wait_runs_out": [_P, c_int, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -121,17 +122,34 @@ class Kernels:
             raise KernelError(f"{what}: {detail}")
 
     def check(self) -> None:
-        """Raise if a kernel flagged bad input (a token id or position out of range)."""
+        """Read the kernels' error word; if a kernel flagged bad input (a token id or position out of
+        range: the row was zeroed or skipped) or gave up on a bounded wait since the last look, clear
+        the word and raise. The results of the step that raised it are not to be used. The generation
+        loop reads the word with every step's tokens, the step function at the end of every
+        multi-token step."""
         flag = int(self.error.item())
         if flag:
             self.error.zero_()
-            raise KernelError({1: "a token id outside the embedding table reached the device",
-                               2: "a position outside the rotary table reached the device",
-                               3: "a tensor-core GEMM gave up waiting for a free shared-memory stage",
-                               4: "a tensor-core GEMM gave up waiting for a TMA load",
-                               5: "a tensor-core GEMM gave up waiting for its accumulator"}.get(
-                                   flag, f"a tensor-core attention kernel gave up on a barrier wait (code {flag})"
-                                   if 6 <= flag <= 10 else f"flag {flag}"))
+            raise KernelError(self.describe(flag))
+
+    @staticmethod
+    def describe(flag: int) -> str:
+        known = {1: "a token id outside the embedding table reached the device",
+                 2: "a position outside the rotary table reached the device",
+                 3: "a tensor-core GEMM gave up waiting for a free shared-memory stage",
+                 4: "a tensor-core GEMM gave up waiting for a TMA load",
+                 5: "a tensor-core GEMM gave up waiting for its accumulator",
+                 21: "the wait of the self-test kernel ran out (as it is meant to)"}
+        if flag in known:
+            return known[flag]
+        if 6 <= flag <= 14:
+            return f"the tensor-core attention kernel gave up on a barrier wait (code {flag})"
+        return f"error flag {flag}"
+
+    def selftest_wait_runs_out(self, limit_us: int = 1000) -> None:
+        """Launch a kernel whose only wait, on a barrier nobody arrives at, runs out after ``limit_us``
+        and sets the error word; ``check`` then raises. For the tests of the error path."""
+        self._ok(self.core.krk_selftest_wait_runs_out(self.error.data_ptr(), int(limit_us), self._stream()), "self-test wait")
 
     def empty_like(self, x):
         return torch.empty_like(x)

@@ -204,3 +204,24 @@ KRK_API int krk_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N
   if (variant == 1) return launch<false, 128, 3, bf16>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
   return launch<false, 256, 4, bf16>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
 }
+
+// A wait that runs out, for the tests of the error path: one thread waits, with a short limit, on a
+// barrier at which nothing ever arrives, then reports as every bounded wait of these kernels does:
+// it writes its code into the error word and returns. Nothing faults and nothing spins without limit.
+namespace {
+__global__ void wait_runs_out_kernel(int* error, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!tc::mbar_wait(&bar, 0, limit_ns)) atomicExch(error, 21);
+  }
+}
+}  // namespace
+
+KRK_API int krk_selftest_wait_runs_out(int* error, int limit_us, cudaStream_t stream) {
+  if (limit_us < 1 || limit_us > 100000) return -2;
+  wait_runs_out_kernel<<<1, 32, 0, stream>>>(error, (unsigned long long)limit_us * 1000ull);
+  KRK_CHECK_LAUNCH();
+  return 0;
+}

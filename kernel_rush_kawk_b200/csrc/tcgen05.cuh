@@ -24,7 +24,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 // Bounded wait on a phase parity; false if it gave up. The clock is read once in 256 polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   const uint32_t addr = smem_u32(bar);
   unsigned long long t0 = 0;
   for (uint32_t i = 1;; ++i) {
@@ -40,7 +40,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((i & 255u) == 0) {
       const unsigned long long now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
 }

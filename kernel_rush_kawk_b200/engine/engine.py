@@ -8,7 +8,9 @@ token (EOS is an ordinary id), exactly ``max_new_tokens`` yields. Keyword
 options add what the reference lacks: unequal prompt lengths need no option;
 ``temperature`` and ``seed`` sample; ``stop_token_ids`` end a sequence early (its
 place then holds None); ``dtype`` picks the bfloat16 serving path or the true
-float32 path.
+float32 path. After a call ``Engine.last_stats`` holds the batch's times (the
+reference logs the like: engine/engine.py:206,378); a kernel that flagged bad
+input or gave up on a wait makes the call raise ``KernelError``.
 
 Like the reference, which turns TF32 off at construction (engine.py:481-482),
 the engine forbids reduced-precision matrix modes for the library products it
@@ -25,7 +27,7 @@ from pathlib import Path
 import torch
 
 from ..cache.store import PAGE, SequenceCache
-from ..config.registry import get_architecture, read_config
+from ..config.registry import get_architecture, preset_config, read_config
 from ..sampling.sampler import Sampler, SamplingParams
 from ..weights.loader import read_checkpoint
 from ..weights.random_init import random_tensors
@@ -63,7 +65,7 @@ def _default_ops(device: torch.device, head_dims):
 class Engine:
     def __init__(self, model_path=None, *, dtype="bfloat16", max_tokens: int | None = None, max_slots: int = 64,
                  max_context: int | None = None, use_cuda_graphs: bool = True, max_step_rows: int = 16384,
-                 device="cuda:0", ops=None, _config=None, _tensors=None):
+                 step_tokens: int = 2048, device="cuda:0", ops=None, _config=None, _tensors=None):
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
@@ -97,8 +99,12 @@ class Engine:
         # the reference's own switch, same name and meaning (engine/engine.py:487)
         self.use_cuda_graphs = bool(use_cuda_graphs) and os.environ.get("ENGINE_NO_GRAPHS") is None
         self.max_step_rows = max_step_rows
+        # the most tokens of one sequence in one pass where a layer keeps a window of keys: it sizes that
+        # layer's ring of pages (window + step_tokens positions); longer steps are cut into passes
+        self.step_tokens = int(step_tokens)
         self.cache = self.stepper = self.loop = None
         self.sampler = Sampler(self.ops, self.device)
+        self.last_stats = None  # GenerationStats of the last batch that generate / generate_all ran
         if max_tokens is not None:
             self._build_cache(int(max_tokens), self.max_slots)
         log.info("engine ready in %.1fs (%s, %s)", time.perf_counter() - t0, self.plan.architecture, self.dtype)
@@ -109,8 +115,7 @@ class Engine:
         """Random weights for a configuration (an instance, or a preset's name), drawn
         on the engine's device from (tensor name, seed)."""
         if isinstance(config, str):
-            from ..config.qwen3 import Qwen3Config
-            config = Qwen3Config.preset(config)
+            config = preset_config(config)
         arch = get_architecture(config.architecture)
         device = torch.device(options.get("device", "cuda:0"))
         expected = PartTree(arch.plan(config)).expected_tensors()
@@ -118,11 +123,14 @@ class Engine:
         return cls(None, _config=config, _tensors=tensors, **options)
 
     def _build_cache(self, max_tokens: int, max_slots: int) -> None:
+        if self.cache is not None and self.cache.live:
+            raise RuntimeError(f"the cache cannot be rebuilt while {self.cache.live} sequences are live in it "
+                               "(an earlier generate() is still open: finish or close it first)")
         self.cache = self.stepper = self.loop = None  # drop the old storage and graphs first
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
         self.cache = SequenceCache(self.model.cache_needs(), max_tokens, max_slots, self.max_context, self.device,
-                                   self.dtype)
+                                   self.dtype, step_tokens=self.step_tokens)
         self.stepper = Stepper(self.model, self.cache, self.ops, self.max_step_rows, self.use_cuda_graphs)
         self.loop = GenerationLoop(self.stepper, self.cache, self.sampler)
 
@@ -149,17 +157,27 @@ class Engine:
                 raise ValueError(f"a prompt of {len(row)} tokens plus {max_new_tokens} new ones exceeds "
                                  f"the context of {self.max_context}")
         self._ensure_cache([len(p) for p in prompts], max_new_tokens)
-        yield from self.loop.run_batch(prompts, max_new_tokens, SamplingParams(temperature, seed), stop_token_ids)
+        try:
+            yield from self.loop.run_batch(prompts, max_new_tokens, SamplingParams(temperature, seed), stop_token_ids)
+        finally:
+            self.last_stats = self.loop.stats
+            log.info("generate: %s", self.last_stats.line())
 
     def generate_all(self, input_ids, max_new_tokens: int, *, temperature: float = 0.0, seed: int = 0,
                      stop_token_ids=(), max_batch: int | None = None) -> list:
         """Any number of requests, run as consecutive batches; returns each request's tokens."""
         prompts = [list(map(int, row)) for row in input_ids]
-        if self.cache is None:
+        if not prompts or max_new_tokens < 1:
+            return [[] for _ in prompts]
+        if self.max_tokens is None:  # no fixed size: room for the largest batch these requests can form
             lens = sorted((len(p) for p in prompts), reverse=True)[:max_batch or self.max_slots]
             self._ensure_cache(lens, max_new_tokens)
-        return self.loop.run_requests(prompts, max_new_tokens, SamplingParams(temperature, seed), stop_token_ids,
-                                      max_batch)
+        try:
+            return self.loop.run_requests(prompts, max_new_tokens, SamplingParams(temperature, seed), stop_token_ids,
+                                          max_batch)
+        finally:
+            self.last_stats = self.loop.stats
+            log.info("generate_all, last batch: %s", self.last_stats.line())
 
     # -- lower level, for replay and tests --------------------------------------
     def open_cache(self, max_tokens: int, max_slots: int | None = None) -> None:

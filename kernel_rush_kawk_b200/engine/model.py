@@ -17,10 +17,7 @@ import torch
 
 from ..parts import base as parts_base
 from ..parts.base import KVNeed, StateNeed, Stream, TensorSpec
-from ..parts.embedding import OutputHead, TokenEmbedding
 from ..parts.plan import ModelPlan, PartSpec
-
-_FIXED_KINDS = {"token_embedding": TokenEmbedding, "output_head": OutputHead}
 
 
 @dataclass
@@ -50,8 +47,8 @@ class PartTree:
 
         self.plan = plan
         positions = min(plan.max_positions, max_context) if max_context else plan.max_positions
-        self.embedding = _build(plan.embedding, _FIXED_KINDS.__getitem__)
-        self.head = _build(plan.head, _FIXED_KINDS.__getitem__)
+        self.embedding = _build(plan.embedding, parts_base.embedding_class)
+        self.head = _build(plan.head, parts_base.head_class)
         self.final_norm = _build(plan.final_norm, parts_base.norm_class)
         self.position = None
         if plan.position is not None:

@@ -62,7 +62,6 @@ class BatchMeta:
         self.host_np = self.host.numpy()
         self._host_views = {name: self.host_np[off:off + size] for name, off, size in zip(self.FIELDS, offsets, sizes)}
         self._single_token_shape = False  # the pinned buffer holds the constant arrays of a one-token-each pass
-        self.places = None  # (slots, starts) that the pinned buffer was prepared for, tokens still to come
         for name, off, size in zip(self.FIELDS, offsets, sizes):
             setattr(self, name, self.buffer[off:off + size])
         self.copied = torch.cuda.Event() if self.buffer.is_cuda else None
@@ -78,12 +77,10 @@ class BatchMeta:
     def host_field(self, name: str) -> np.ndarray:
         return self._host_views[name]
 
-    def fill(self, slots, starts, token_lists, want_rows, upload: bool = True) -> None:
-        """Write one pass into the pinned buffer and start its copy to the device (``upload``
-        False: the copy waits for ``fill_tokens``)."""
+    def fill(self, slots, starts, token_lists, want_rows) -> None:
+        """Write one pass into the pinned buffer and start its copy to the device."""
         if self.copied is not None:
             self.copied.synchronize()  # the previous copy out of this pinned buffer is over
-        self.places = None
         q_lens = [len(t) for t in token_lists]
         view = self._host_views
         if self.n_rows == self.n_seqs:
@@ -108,8 +105,7 @@ class BatchMeta:
         view["seq_slot"][:] = slots
         view["seq_start"][:] = starts
         view["want"][:] = want_rows
-        if upload:
-            self.upload()
+        self.upload()
         self.max_q_len = max(q_lens)
         self.max_kv_len = max(s + n for s, n in zip(starts, q_lens))
         self.is_decode = self.max_q_len == 1
@@ -120,12 +116,6 @@ class BatchMeta:
         self.buffer.copy_(self.host, non_blocking=True)
         if self.copied is not None:
             self.copied.record()
-
-    def fill_tokens(self, token_lists) -> None:
-        """The tokens of a one-token-each pass whose places are in the pinned buffer already."""
-        self._host_views["tokens"][:] = [t[0] for t in token_lists]
-        self.places = None
-        self.upload()
 
     @property
     def bytes(self) -> int:
@@ -147,6 +137,78 @@ class _DecodeGraph:
         self.graph, self.meta, self.logits = graph, meta, logits
 
 
+class DecodeRun:
+    """Single-token steps of a fixed set of sequences, queued ahead of the host.
+
+    ``launch`` queues one step: page reservation, the captured step, the selection kernel, which
+    also writes the chosen tokens and the positions of the next step into the step's batch
+    description on the device, and a copy of the tokens (and of the kernels' error word) into a
+    ring of pinned rows, fenced by an event. ``collect`` waits for the oldest queued step and
+    returns its tokens. At most ``depth`` steps are queued. The reference's ``GraphPlan.run``
+    works the same way (engine/engine.py:81-83,458-469 of willzeng274/kernel-rush-kawk)."""
+
+    def __init__(self, stepper, slots, tokens, sampling, requests, first_step: int, depth: int):
+        self.stepper, self.slots, self.sampling = stepper, slots, sampling
+        self.depth = max(1, depth)
+        n = self.n = len(slots)
+        cache, dev = stepper.cache, stepper.device
+        starts = [cache.length[s] for s in slots]
+        for s, start in zip(slots, starts):
+            cache.reserve(s, start + 1)
+        cache.sync()
+        token_lists = [[t] for t in tokens]
+        self.graph = stepper._graphs.get(n) or stepper._capture(n, slots, starts, token_lists)
+        self.graph.meta.fill(slots, starts, token_lists, list(range(n)))
+        stepper.h2d_bytes = self.graph.meta.bytes
+        ring = stepper._run_rings.get((n, self.depth))
+        if ring is None:
+            if len(stepper._run_rings) > 64:
+                stepper._run_rings.clear()
+            ring = stepper._run_rings[(n, self.depth)] = (
+                torch.empty((self.depth, n), dtype=torch.int32, device=dev),
+                torch.empty((self.depth, n + 1), dtype=torch.int32, pin_memory=True),
+                [torch.cuda.Event() for _ in range(self.depth)])
+        self.device_tokens, self.host_tokens, self.events = ring
+        self.requests = torch.tensor(requests, dtype=torch.int32).to(dev)
+        self.step = first_step
+        self.launched = self.collected = 0
+
+    @property
+    def in_flight(self) -> int:
+        return self.launched - self.collected
+
+    def launch(self) -> None:
+        if self.in_flight >= self.depth:
+            raise RuntimeError(f"{self.depth} steps are queued already; collect one first")
+        st, cache, n = self.stepper, self.stepper.cache, self.n
+        if self.launched:  # the first step's pages were reserved with the batch description
+            for s in self.slots:
+                cache.reserve(s, cache.length[s] + 1)
+            cache.sync()
+        k = self.launched % self.depth
+        self.graph.graph.replay()
+        st.ops.select_tokens(self.graph.logits, float(self.sampling.temperature), int(self.sampling.seed), self.requests,
+                             self.step + self.launched, feed=self.graph.meta, out=self.device_tokens[k])
+        self.host_tokens[k, :n].copy_(self.device_tokens[k], non_blocking=True)
+        self.host_tokens[k, n:].copy_(st.ops.error, non_blocking=True)
+        self.events[k].record()
+        for s in self.slots:
+            cache.advance(s, 1)
+        st.passes += 1
+        self.launched += 1
+
+    def collect(self) -> list:
+        if self.in_flight == 0:
+            raise RuntimeError("no step is queued")
+        k = self.collected % self.depth
+        self.events[k].synchronize()
+        row = self.host_tokens[k].tolist()
+        self.collected += 1
+        if row[-1]:
+            self.stepper.ops.check()  # raises with the flag's meaning and clears the word
+        return row[:-1]
+
+
 class Stepper:
     def __init__(self, model, cache: SequenceCache, ops, max_step_rows: int = 16384, use_graphs: bool = True):
         self.model = model
@@ -161,17 +223,18 @@ class Stepper:
         self.graph_launches: dict[int, int] = {}  # kernels of this package inside each captured step
         self.h2d_bytes = 0  # bytes of the last step's host-to-device copies
         self.passes = 0
+        self._run_rings: dict = {}  # (sequences, depth) -> token ring of a DecodeRun, reused by later runs
 
     # ------------------------------------------------------------------
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         if not entries:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
         self._validate(entries)
-        per_seq = self.cache.step_tokens if any(
-            g.need.window is not None for g in self.cache._kv_groups) else self.max_step_rows
+        per_seq = min(self.max_step_rows, self.cache.per_sequence_step_limit() or self.max_step_rows)
         done = [0] * len(entries)
         pieces, order = [], []
         self.h2d_bytes = 0
+        many = any(len(e.tokens) > 1 for e in entries)
         while True:
             rows_left = self.max_step_rows
             chosen = []
@@ -190,6 +253,8 @@ class Stepper:
                 order.extend(which)
             for i, _, n in chosen:
                 done[i] += n
+        if many and hasattr(self.ops, "check"):
+            self.ops.check()  # a multi-token step ends with a look at the kernels' error word
         wanted = [(i, w) for i, e in enumerate(entries) for w in e.want]
         if not wanted:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
@@ -270,31 +335,11 @@ class Stepper:
         return None
 
     # -- decode from a captured graph ------------------------------------------
-    def prepare_single_tokens(self, slots) -> None:
-        """The host's share of the next step, if that step brings one token for each of ``slots``
-        (in this order): page reservation, page-table upload, positions and slots in the pinned
-        batch description. Everything here is independent of the tokens, so a caller does it while
-        the device still computes them. A step with other slots simply ignores the preparation."""
-        n = len(slots)
-        g = self._graphs.get(n) if self.use_graphs else None
-        if g is None:
-            return
-        cache = self.cache
-        starts = [cache.length[s] for s in slots]
-        for s, start in zip(slots, starts):
-            cache.reserve(s, start + 1)
-        cache.sync()
-        g.meta.fill(slots, starts, [[0]] * n, list(range(n)), upload=False)
-        g.meta.places = (list(slots), starts)
-
     def _replay(self, slots, starts, token_lists, want_rows, n: int):
         g = self._graphs.get(n)
         if g is None:
             g = self._capture(n, slots, starts, token_lists)
-        if g.meta.places == (slots, starts):
-            g.meta.fill_tokens(token_lists)
-        else:
-            g.meta.fill(slots, starts, token_lists, list(range(n)))
+        g.meta.fill(slots, starts, token_lists, list(range(n)))
         self.h2d_bytes += g.meta.bytes
         g.graph.replay()
         if len(want_rows) == n:
@@ -338,6 +383,13 @@ class Stepper:
             cache.advance(s, n_steps)
         self.passes += n_steps
         return out
+
+    def open_decode_run(self, slots, tokens, sampling, requests, first_step: int, depth: int = 3):
+        """A ``DecodeRun`` over these sequences, or None where single-token steps cannot be queued
+        ahead of the host (no captured graph: graphs are off, or a part reads the step on the host)."""
+        if not self.use_graphs or not slots:
+            return None
+        return DecodeRun(self, list(slots), [int(t) for t in tokens], sampling, list(requests), int(first_step), int(depth))
 
     def _capture(self, n: int, slots, starts, token_lists) -> _DecodeGraph:
         meta = BatchMeta(n, n, n, self.device)

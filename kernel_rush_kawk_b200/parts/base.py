@@ -10,6 +10,9 @@ Registries map a kind name to a class, so that a plan can choose a part layer
 by layer and so that a new part can be added without touching this package:
 
     register_mixer("my_mixer", MyMixer)
+
+The same holds for the two parts that stand outside the layers, the embedding of
+the tokens and the output head (``register_embedding``, ``register_head``).
 """
 
 from __future__ import annotations
@@ -82,6 +85,19 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    def forward(self, ctx):
+        """The step's rows [rows, hidden] from ``ctx.batch.tokens``."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, ctx, h):
+        """h: the normalised rows of the wanted positions (a tensor, or a norm's lazy result)
+        -> float32 logits [rows, vocab]."""
+        raise NotImplementedError
+
+
 class Mixer(Part):
     def cache_need(self):
         """KVNeed, StateNeed or None."""
@@ -147,6 +163,8 @@ _FEED_FORWARDS: dict[str, type] = {}
 _NORMS: dict[str, type] = {}
 _POSITIONS: dict[str, type] = {}
 _BLOCKS: dict[str, type] = {}
+_EMBEDDINGS: dict[str, type] = {}
+_HEADS: dict[str, type] = {}
 
 
 def _register(table: dict, what: str):
@@ -171,9 +189,13 @@ register_feed_forward = _register(_FEED_FORWARDS, "feed-forward")
 register_norm = _register(_NORMS, "norm")
 register_position = _register(_POSITIONS, "position encoding")
 register_block = _register(_BLOCKS, "block arrangement")
+register_embedding = _register(_EMBEDDINGS, "embedding")
+register_head = _register(_HEADS, "output head")
 
 mixer_class = _lookup(_MIXERS, "mixer")
 feed_forward_class = _lookup(_FEED_FORWARDS, "feed-forward")
 norm_class = _lookup(_NORMS, "norm")
 position_class = _lookup(_POSITIONS, "position encoding")
 block_class = _lookup(_BLOCKS, "block arrangement")
+embedding_class = _lookup(_EMBEDDINGS, "embedding")
+head_class = _lookup(_HEADS, "output head")

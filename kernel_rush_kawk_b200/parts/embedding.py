@@ -7,10 +7,10 @@ head is tied (engine/model.py:103-107,303). Logits leave in 32-bit.
 
 from __future__ import annotations
 
-from .base import Part, TensorSpec
+from .base import Embedding, Head, TensorSpec, register_embedding, register_head
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     """params: vocab, hidden."""
 
     def __init__(self, params):
@@ -29,7 +29,7 @@ class TokenEmbedding(Part):
         return ctx.ops.embed(self.table, ctx.batch.tokens, ctx.batch.n_rows)
 
 
-class OutputHead(Part):
+class OutputHead(Head):
     """params: vocab, hidden. The plan points "weight" at the embedding table's
     checkpoint name when the head is tied."""
 
@@ -48,3 +48,7 @@ class OutputHead(Part):
     def forward(self, ctx, h):
         """h: normalised rows (a Normed or a tensor) of the wanted positions."""
         return ctx.ops.linear(h, self.weight, out_float32=True)
+
+
+register_embedding("token_embedding", TokenEmbedding)
+register_head("output_head", OutputHead)

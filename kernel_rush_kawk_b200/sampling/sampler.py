@@ -54,13 +54,21 @@ class Sampler:
             self._requests_host = list(requests)
             self._requests = torch.tensor(requests, dtype=torch.int32).to(self.device)
         tokens = self.ops.select_tokens(logits, float(params.temperature), int(params.seed), self._requests, int(step))
-        if self._pinned is None or self._pinned.numel() < n:
-            self._pinned = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=self.device.type == "cuda")
-        host = self._pinned[:n]
-        host.copy_(tokens, non_blocking=True)
+        if self._pinned is None or self._pinned.numel() < n + 1:
+            self._pinned = torch.empty(max(n, 64) + 1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        host = self._pinned[:n + 1]
+        host[:n].copy_(tokens, non_blocking=True)
+        error = getattr(self.ops, "error", None)  # the kernels' error word rides along with the tokens
+        if error is not None:
+            host[n:].copy_(error, non_blocking=True)
+        else:
+            host[n] = 0
         return host
 
     def finish(self, host) -> list[int]:
         if self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
-        return host.tolist()
+        row = host.tolist()
+        if row[-1]:
+            self.ops.check()  # raises with the flag's meaning and clears the word
+        return row[:-1]

@@ -30,7 +30,7 @@ def pytest_collection_modifyitems(config, items):
 def folders(tmp_path_factory):
     """Model folders of the tiny configurations, written once per session into a
     temporary directory: name -> path."""
-    from helpers import TINY, write_tiny
+    from helpers import EXTRA, TINY, write_tiny
 
     root = tmp_path_factory.mktemp("models")
-    return {name: write_tiny(root / name, name) for name in TINY}
+    return {name: write_tiny(root / name, name) for name in TINY + EXTRA}

@@ -6,10 +6,13 @@ Two tiny Qwen3 configurations that differ in every size and option:
   tiny_a      2     64     4    2     16      192   256   1e4    1e-6   tied    none
   tiny_b      3     96     6    2     32      256   384   1e6    1e-5   untied  none
   tiny_w      3     80     5    1     48      144   301   5e5    1e-5   untied  24 keys on layers 1, 2
+  tiny_v      2     96     4    2     64      160   333   1e4    1e-6   tied    70 keys on both layers
 
 tiny_a and tiny_b are the presets of the package; tiny_w adds sizes that are no
 power of two (hidden 80, 5 heads in one group, head size 48, vocabulary 301)
-and layers that see a window of keys only.
+and layers that see a window of keys only. tiny_v (not in ``TINY``: only the tests of long
+windowed sequences use it) has the head size 64 of the tensor-core kernels and a window on every
+layer, so that with a small ``step_tokens`` its ring of pages is shorter than its sequences.
 
 Tolerances, fixed before any measurement:
 * 32-bit path against the plain implementation run in float64:
@@ -44,14 +47,22 @@ TINY_W = {
     "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "tie_word_embeddings": False, "max_position_embeddings": 2048,
     "sliding_window": 24, "layer_types": ["full_attention", "sliding_attention", "sliding_attention"],
 }
+TINY_V = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 96, "intermediate_size": 160,
+    "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 333,
+    "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "tie_word_embeddings": True, "max_position_embeddings": 2048,
+    "sliding_window": 70, "layer_types": ["sliding_attention", "sliding_attention"],
+}
 TINY = ("tiny_a", "tiny_b", "tiny_w")
-SEEDS = {"tiny_a": 11, "tiny_b": 22, "tiny_w": 33}
+EXTRA = ("tiny_v",)
+SEEDS = {"tiny_a": 11, "tiny_b": 22, "tiny_w": 33, "tiny_v": 44}
+_DICTS = {"tiny_w": TINY_W, "tiny_v": TINY_V}
 
 
 def tiny_config(name: str):
     from kernel_rush_kawk_b200 import Qwen3Config
 
-    return Qwen3Config.from_dict(TINY_W) if name == "tiny_w" else Qwen3Config.preset(name)
+    return Qwen3Config.from_dict(_DICTS[name]) if name in _DICTS else Qwen3Config.preset(name)
 
 
 def write_tiny(folder, name: str) -> Path:
@@ -121,3 +132,26 @@ def first_wrong_row(got: torch.Tensor, ref: torch.Tensor, dtype: str):
     tol = tolerance(scale, dtype)
     bad = ((got.float().cpu() - ref.float().cpu()).abs() > tol).any(dim=-1).nonzero()
     return None if bad.numel() == 0 else int(bad[0])
+
+
+def greedy_gap_allowed(cfg, w, seq, dtype: str, windows=None):
+    """(reference logits at the last position of ``seq``, the gap below their maximum that a greedy
+    token may have). In 32-bit the reference is the plain implementation in float64 and the gap is the
+    32-bit tolerance. In bfloat16 the gap is the noise of bfloat16 arithmetic measured at this very
+    position: twice the spread between the plain implementation's logits with float32 and with float64
+    accumulation (same rounding points, two orders of summation), plus one bfloat16 step (2^-7) of
+    the largest logit for the one-ulp flips that two correct implementations may differ by."""
+    if dtype == "float32":
+        ref = plain.forward_logits(cfg, w, seq, torch.float64, None, windows)[-1].float()
+        return ref, 2 * FP32_TOL * ref.abs().max().item()
+    a = plain.forward_logits(cfg, w, seq, torch.float32, torch.bfloat16, windows)[-1]
+    b = plain.forward_logits(cfg, w, seq, torch.float64, torch.bfloat16, windows)[-1].float()
+    return a, 2 * (a - b).abs().max().item() + a.abs().max().item() / 128
+
+
+def assert_greedy_token(cfg, w, seq, tok: int, dtype: str, windows=None, what: str = "") -> None:
+    """``tok`` continues ``seq`` greedily: it is the plain argmax, or lies below it by no more than
+    ``greedy_gap_allowed``."""
+    ref, allowed = greedy_gap_allowed(cfg, w, seq, dtype, windows)
+    gap = ref.max().item() - ref[tok].item()
+    assert gap <= allowed, f"{what}: token {tok} lies {gap:.4g} below the plain argmax {int(ref.argmax())} (allowed {allowed:.4g})"

@@ -61,8 +61,7 @@ def test_a_step_too_large_for_one_pass_is_cut(folders):
     from kernel_rush_kawk_b200 import StepEntry
 
     name = "tiny_w"  # has window layers: the per-sequence piece is bounded by the ring
-    engine = cpu_engine(folders, name, max_step_rows=48)
-    engine.cache.step_tokens = 40
+    engine = cpu_engine(folders, name, max_step_rows=48, step_tokens=40)
     seqs = prompts_for(name, [100, 30], seed=22)
     slots = [engine.cache.alloc() for _ in seqs]
     before = engine.stepper.passes

@@ -105,3 +105,76 @@ def test_batches_run_one_after_another_and_reuse_slots():
     assert [c[0] for c in sampler.calls if c[1] == 0] == [[0, 1], [2, 3], [4]]
     assert cache.live == 0
     cache.check()
+
+
+class ScriptedRun:
+    """A stand-in for the step function's DecodeRun: steps are "queued" by counting them, and a
+    collected step yields request r's script[r][step]."""
+
+    def __init__(self, owner, slots, requests, first_step, depth):
+        self.owner, self.slots, self.requests, self.step, self.depth = owner, slots, requests, first_step, depth
+        self.launched = self.collected = 0
+
+    @property
+    def in_flight(self):
+        return self.launched - self.collected
+
+    def launch(self):
+        assert self.in_flight < self.depth
+        for s in self.slots:
+            self.owner.cache.reserve(s, self.owner.cache.length[s] + 1)
+            self.owner.cache.advance(s, 1)
+        self.launched += 1
+        self.owner.most_in_flight = max(self.owner.most_in_flight, self.in_flight)
+
+    def collect(self):
+        step = self.step + self.collected
+        self.collected += 1
+        self.owner.collected.append((list(self.requests), step))
+        return [self.owner.script[r][step] for r in self.requests]
+
+
+class RunAheadStepper(ScriptedStepper):
+    def __init__(self, cache, script):
+        super().__init__(cache)
+        self.script, self.runs, self.collected, self.most_in_flight = script, [], [], 0
+
+    def open_decode_run(self, slots, tokens, sampling, requests, first_step, depth):
+        self.runs.append((list(requests), list(tokens), first_step))
+        return ScriptedRun(self, list(slots), list(requests), first_step, depth)
+
+
+def make_ahead(script, max_slots=4):
+    cache = SequenceCache([KVNeed(1, 8)], 64 * 16, max_slots, 64 * 8, "cpu", torch.float32)
+    stepper = RunAheadStepper(cache, script)
+    return GenerationLoop(stepper, cache, ScriptedSampler(script)), cache, stepper
+
+
+def test_steps_run_ahead_of_the_consumer_and_never_past_the_last_token():
+    loop, cache, stepper = make_ahead({0: list(range(10, 17)), 1: list(range(20, 27))})
+    out = list(loop.run_batch([[1, 2], [3]], 7))
+    assert out == [[10 + t, 20 + t] for t in range(7)]
+    assert stepper.runs == [([0, 1], [10, 20], 1)]  # one run from the first tokens on
+    assert stepper.most_in_flight == GenerationLoop.RUN_AHEAD
+    assert [c[1] for c in stepper.collected] == [1, 2, 3, 4, 5, 6]  # the seventh token is never fed back
+    assert cache.live == 0 and max(cache.length) == 0
+    cache.check()
+
+
+def test_a_stop_read_late_drops_what_ran_ahead_for_that_sequence_only():
+    """Request 0 stops at step 2. Steps 3 and 4 were queued before the host read that: request 1's
+    tokens from them count, request 0's are dropped, and a new run goes on with request 1 alone."""
+    script = {0: [5, 6, 99, 1, 2, 3, 4, 5], 1: [7, 8, 9, 10, 11, 12, 13, 14]}
+    loop, cache, stepper = make_ahead(script)
+    out = list(loop.run_batch([[1], [2]], 8, stop_token_ids=[99]))
+    assert out == [[5, 7], [6, 8], [99, 9], [None, 10], [None, 11], [None, 12], [None, 13], [None, 14]]
+    assert stepper.runs[0] == ([0, 1], [5, 7], 1)
+    assert stepper.runs[1][0] == [1] and stepper.runs[1][1] == [script[1][stepper.runs[1][2] - 1]]
+    assert cache.live == 0
+    cache.check()
+
+
+def test_a_lone_sequence_that_stops_yields_nothing_after_its_stop():
+    loop, cache, stepper = make_ahead({0: [1, 99, 3, 4, 5, 6]})
+    assert list(loop.run_batch([[4]], 6, stop_token_ids=[99])) == [[1], [99]]
+    assert cache.live == 0

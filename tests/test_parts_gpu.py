@@ -166,8 +166,27 @@ def test_swiglu_part_and_block_alone(dtype):
 # ---------------------------------------------------------------------------------
 def register_toy():
     from kernel_rush_kawk_b200.config import ModelConfig, register_architecture
-    from kernel_rush_kawk_b200.parts import (LayerSpec, Mixer, ModelPlan, PartSpec, ScheduleEntry, StateNeed, TensorSpec,
-                                             register_mixer)
+    from kernel_rush_kawk_b200.parts import (Embedding, LayerSpec, Mixer, ModelPlan, PartSpec, ScheduleEntry, StateNeed,
+                                             TensorSpec, register_embedding, register_mixer)
+
+    class ScaledEmbedding(Embedding):
+        """x0[r] = round(table[ids[r]] * scale): an embedding kind of the test's own."""
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.vocab, self.hidden, self.scale = int(params["vocab"]), int(params["hidden"]), float(params["scale"])
+
+        def tensor_specs(self):
+            return {"table": TensorSpec((self.vocab, self.hidden), "table")}
+
+        def bind(self, tensors, runtime):
+            self.table = tensors["table"]
+
+        def forward(self, ctx):
+            x = ctx.ops.embed(self.table, ctx.batch.tokens, ctx.batch.n_rows)
+            return (x.float() * self.scale).to(x.dtype)
+
+    register_embedding("test_scaled_embedding", ScaledEmbedding)
 
     class DecayMixer(Mixer):
         """s_t = decay * s_{t-1} + h_t (state [hidden] per sequence, float32); out_t = s_t W^T."""
@@ -215,6 +234,15 @@ def register_toy():
         def to_dict(self):
             return {"architectures": [self.architecture], "hidden": self.hidden, "vocab": self.vocab}
 
+        @classmethod
+        def preset_names(cls):
+            return ["toy_small"]
+
+        @classmethod
+        def preset(cls, name):
+            assert name == "toy_small"
+            return cls(48, 61)
+
     def plan(cfg):
         H = cfg.hidden
         norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": name})
@@ -233,7 +261,7 @@ def register_toy():
         # queries only that reads the keys and values of the second run of layer 0
         schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, cache_from=2)]
         return ModelPlan("ToyDecoderForTests", H, cfg.vocab,
-                         PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": H}, {"table": "embed"}),
+                         PartSpec("test_scaled_embedding", {"vocab": cfg.vocab, "hidden": H, "scale": 3.0}, {"table": "embed"}),
                          PartSpec("rope", {"theta": 1e4, "dim": 16}), tuple(layers), tuple(schedule), norm("final"),
                          PartSpec("output_head", {"vocab": cfg.vocab, "hidden": H}, {"weight": "embed"}), 512)
 
@@ -247,7 +275,7 @@ def toy_plain(w, ids, rounding):
     T = len(ids)
     cos, sin = plain.rope_tables(16, 1e4, T, torch.float32, rounding)
     cfg = SimpleNamespace(heads=4, kv_heads=2, head_dim=16, eps=1e-5)
-    x = w["embed"][torch.tensor(ids)]
+    x = rt(w["embed"][torch.tensor(ids)] * 3.0)
 
     def attn(h, i, kv=None):
         q = plain.linear(h, w[f"l{i}.attn.q_proj"], rounding).view(T, 4, 16)
@@ -319,6 +347,11 @@ def test_toy_architecture_with_a_state_mixer_a_repeated_layer_and_a_shared_cache
     engine.cache.check()
     toks = list(engine.generate([seqs[1]], 3))
     assert len(toks) == 3
+    # the architecture's own preset, by name, through the registry: random weights, a few tokens
+    from kernel_rush_kawk_b200.config import preset_config
+    assert preset_config("toy_small").vocab == 61
+    small = Engine.from_random("toy_small", seed=1, std=0.08, dtype=NAME[dtype], max_slots=2)
+    assert small.plan.vocab_size == 61 and len(list(small.generate([[1, 2, 3]], 2))) == 2
 
 
 # ---------------------------------------------------------------------------------
@@ -328,8 +361,27 @@ def test_toy_architecture_with_a_state_mixer_a_repeated_layer_and_a_shared_cache
 # ---------------------------------------------------------------------------------
 def register_routed_toy():
     from kernel_rush_kawk_b200.config import ModelConfig, register_architecture
-    from kernel_rush_kawk_b200.parts import (FeedForward, LayerSpec, ModelPlan, PartSpec, PositionEncoding, ScheduleEntry,
-                                             TensorSpec, register_feed_forward, register_position)
+    from kernel_rush_kawk_b200.parts import (FeedForward, Head, LayerSpec, ModelPlan, PartSpec, PositionEncoding,
+                                             ScheduleEntry, TensorSpec, register_feed_forward, register_head,
+                                             register_position)
+
+    class CappedHead(Head):
+        """logits = cap * tanh((h W^T) / cap), in 32-bit: an output head of the test's own."""
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.vocab, self.hidden, self.cap = int(params["vocab"]), int(params["hidden"]), float(params["cap"])
+
+        def tensor_specs(self):
+            return {"weight": TensorSpec((self.vocab, self.hidden), "table")}
+
+        def bind(self, tensors, runtime):
+            self.weight = tensors["weight"]
+
+        def forward(self, ctx, h):
+            return self.cap * torch.tanh(ctx.ops.linear(h, self.weight, out_float32=True) / self.cap)
+
+    register_head("test_capped_head", CappedHead)
 
     class LearnedPositions(PositionEncoding):
         """x_t += table[position of t]; queries and keys are not rotated."""
@@ -413,7 +465,7 @@ def register_routed_toy():
                          PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": H}, {"table": "embed"}),
                          PartSpec("test_learned_positions", {"table_rows": 256, "hidden": H}, {"table": "positions"}),
                          tuple(layers), (ScheduleEntry(0), ScheduleEntry(1)), norm("final"),
-                         PartSpec("output_head", {"vocab": cfg.vocab, "hidden": H}, {"weight": "head"}), 256)
+                         PartSpec("test_capped_head", {"vocab": cfg.vocab, "hidden": H, "cap": 2.0}, {"weight": "head"}), 256)
 
     register_architecture("ToyRoutedForTests", RoutedConfig, plan)
     return RoutedConfig()
@@ -445,7 +497,8 @@ def routed_plain(w, ids, rounding):
             y = plain.swiglu_mlp(h[rows], gu[:32], gu[32:], w[f"l{i}.moe.down_{e}"], rounding)
             out[rows] = rt(y * prob[rows, e][:, None])
         x = plain.residual_add(x, out, rounding)
-    return plain.rms_norm(x, w["final"], 1e-6, rounding) @ w["head"].t(), torch.stack(margins).min(dim=0).values
+    logits = 2.0 * torch.tanh((plain.rms_norm(x, w["final"], 1e-6, rounding) @ w["head"].t()) / 2.0)
+    return logits, torch.stack(margins).min(dim=0).values
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
