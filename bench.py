@@ -11,9 +11,11 @@ at batch 1 and 64 (``points``); a 2,048-token prompt is prefilled (``prefill``).
 
 * ``value``: decoded tokens per second, timed on the device with CUDA events around
   K steps that run without the host in between (captured step + selection kernel,
-  which feeds the next step).
-* ``e2e``: the same through ``Engine.generate``: every step copies its batch
-  description from pinned host memory and reads its tokens back to the host.
+  which feeds the next step); the median of 5 such timed regions, with the clocks
+  sampled during them. ``points`` and ``prefill`` carry clock records of their own.
+* ``e2e``: the same through ``Engine.generate``: host token lists in, and every step's
+  tokens (with the kernels' error word) read back to the host through pinned memory;
+  at batch 8, and at batch 1 and 64 under ``e2e.points``.
 * ``roofline``: bytes a decode step has to read (every weight once, the live
   requests' keys and values at the mean context of the timed steps) over its time,
   against the measured copy bandwidth.
@@ -105,6 +107,32 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def timed_regions(steps_iter, warmup: int, steps: int, counter=None):
+    """Consume a generator of decode steps: `warmup` untimed yields, then REPEATS regions of `steps`
+    yields each, timed by the host's clock from the yield before a region to its last yield. Returns
+    (median ms per step over the regions, mean of `counter`'s growth per step). As with the
+    device-timed figure, the median keeps out the first region, which runs while the board's clocks
+    still recover from the prompt step before it."""
+    for _ in range(warmup):
+        next(steps_iter)
+    before = counter() if counter else 0
+    times, total = [], 0
+    for _ in range(REPEATS):
+        t_start = time.perf_counter()
+        n = 0
+        for _ in steps_iter:
+            n += 1
+            if n == steps:
+                break
+        if n:
+            times.append((time.perf_counter() - t_start) * 1000.0 / n)
+            total += n
+    for _ in steps_iter:  # nothing is left unless the generator yields more than asked
+        pass
+    grown = (counter() - before) / max(total, 1) if counter else 0.0
+    return statistics.median(times), grown
+
+
 def model_numbers(cfg, layers: int) -> dict:
     """Parameter bytes a decode step reads and flops per token of the linear layers."""
     H, I, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
@@ -139,10 +167,13 @@ def run_ours(args) -> dict:
     def prompts(n, length):
         return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
 
-    def decode_point(batch: int, steps: int, warmup: int):
-        """Prefill `batch` prompts, then time `steps` device-fed decode steps. Returns
-        (tokens per second, ms per step, launches per step, mean context)."""
+    def decode_point(batch: int, steps: int, warmup: int, repeats: int = REPEATS):
+        """Prefill `batch` prompts, then time `steps` device-fed decode steps, `repeats` times over
+        (the sequences grow on: each repeat starts where the one before ended; the mean context is
+        that of all timed steps). Returns (tokens per second, median ms per step, launches per step,
+        mean context, clock record)."""
         slots = [cache.alloc() for _ in range(batch)]
+        sampler = ClockSampler()
         try:
             for i in range(0, batch, 8):  # prompts go in by eights to bound activation memory
                 chunk = slots[i:i + 8]
@@ -151,20 +182,34 @@ def run_ours(args) -> dict:
             toks = stepper.decode_on_device(slots, first, warmup)
             first = toks[-1].tolist()
             torch.cuda.synchronize()
+            sampler.start()
+            times, done = [], warmup
             before = ops.launches
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            stepper.decode_on_device(slots, first, steps, first_step=warmup)
-            end.record()
-            torch.cuda.synchronize()
-            ms = start.elapsed_time(end) / steps
+            for _ in range(repeats):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                toks = stepper.decode_on_device(slots, first, steps, first_step=done)
+                end.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(end) / steps)
+                first = toks[-1].tolist()
+                done += steps
+            clocks = sampler.stop()
+            ms = statistics.median(times)
             graph_launches = stepper.graph_launches.get(batch, 0)
-            launches = graph_launches + (ops.launches - before) / steps
-            mean_ctx = PROMPT + warmup + (steps + 1) / 2
-            return batch * 1000.0 / ms, ms, launches, mean_ctx
+            launches = graph_launches + (ops.launches - before) / (steps * repeats)
+            mean_ctx = PROMPT + warmup + (steps * repeats + 1) / 2
+            return batch * 1000.0 / ms, ms, launches, mean_ctx, clocks
         finally:
             for s in slots:
                 cache.free(s)
+
+    def e2e_point(batch: int):
+        """The same through ``Engine.generate``: host token lists in, host token lists out every step."""
+        e2e_prompts = prompts(batch, PROMPT)
+        it = engine.generate(e2e_prompts, args.warmup + REPEATS * args.steps)
+        ms, copied = timed_regions(it, args.warmup, args.steps, stepper.h2d_total)
+        return batch * 1000.0 / ms, ms, copied
 
     if args.only:  # one piece only, for profiling runs: prints a short line of its own
         if args.only == "prefill":
@@ -179,44 +224,39 @@ def run_ours(args) -> dict:
                 cache.free(slot)
             return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms_last": round(ms, 3), "layers": layers}
         b = int(args.only.split("_b")[1])
-        v, ms_b, launches, _ = decode_point(b, args.steps, args.warmup)
+        v, ms_b, launches, _, _ = decode_point(b, args.steps, args.warmup, 1)
         return {"only": args.only, "value": round(v, 1), "ms_per_step": round(ms_b, 4), "launches_per_step": launches,
                 "layers": layers}
 
     # -- headline: batch 8 -------------------------------------------------------
-    sampler = ClockSampler()
-    sampler.start()
-    value, ms_step, launches, mean_ctx = decode_point(8, args.steps, args.warmup)
-    clocks = sampler.stop()
+    value, ms_step, launches, mean_ctx, clocks = decode_point(8, args.steps, args.warmup)
     step_bytes = numbers["weight_bytes"] + 8 * mean_ctx * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
 
-    # -- end to end through the entry point, batch 8 -----------------------------------
-    e2e_prompts = prompts(8, PROMPT)
-    it = engine.generate(e2e_prompts, args.warmup + args.steps)
-    for _ in range(args.warmup):
-        next(it)
-    torch.cuda.synchronize()
-    t_start = time.perf_counter()
-    n = 0
-    for _ in it:
-        n += 1
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t_start) * 1000.0 / max(n, 1)
-    e2e = {"value": round(8 * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-           "h2d_bytes_per_step": stepper.h2d_bytes, "d2h_bytes_per_step": 8 * 4}
+    # -- end to end through the entry point ---------------------------------------------
+    # Each step's input is the step before's output, which the selection kernel hands on on the device; what
+    # still travels from the host every step is the page table's growth (averaged here), and every step's
+    # tokens travel back with the kernels' error word. The reference's loop does the same (engine.py:458-469).
+    e2e_value, e2e_ms, e2e_h2d = e2e_point(8)
+    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": round(e2e_h2d, 1), "d2h_bytes_per_step": (8 + 1) * 4, "points": {}}
 
     # -- the other batch sizes -------------------------------------------------------
-    points = {}
+    points, point_clocks = {}, {}
     for b in (1, 64):
-        v, ms_b, _, ctx_b = decode_point(b, args.steps, args.warmup)
+        v, ms_b, _, ctx_b, ck = decode_point(b, args.steps, args.warmup)
         bytes_b = numbers["weight_bytes"] + b * ctx_b * numbers["kv_bytes_per_token"]
         points[f"decode_b{b}"] = round(v, 1)
+        points[f"decode_b{b}_ms"] = round(ms_b, 4)
         points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        point_clocks[f"decode_b{b}"] = ck
+        e2e["points"][f"decode_b{b}"] = round(e2e_point(b)[0], 1)
 
     # -- prefill of 2,048 tokens ---------------------------------------------------------
     prompt = prompts(1, PREFILL_TOKENS)[0]
     times = []
+    sampler = ClockSampler()
+    sampler.start()
     for i in range(args.warmup + 5):
         slot = cache.alloc()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -227,6 +267,7 @@ def run_ours(args) -> dict:
         cache.free(slot)
         if i >= args.warmup:
             times.append(start.elapsed_time(end))
+    point_clocks["prefill"] = sampler.stop()
     pre_ms = statistics.median(times)
     T = PREFILL_TOKENS
     flops = 2 * T * layers * numbers["per_layer"] + 2 * numbers["head"] + layers * 4 * numbers["attn_dim"] * T * (T + 1) / 2
@@ -249,7 +290,8 @@ def run_ours(args) -> dict:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
-        "points": points, "clocks": clocks, "impl": "ours", "load_s": round(time.time() - t0, 1),
+        "points": points, "clocks": clocks, "point_clocks": point_clocks, "repeats": REPEATS, "impl": "ours",
+        "load_s": round(time.time() - t0, 1),
     }
 
 
@@ -318,7 +360,7 @@ def run_reference(args) -> dict:
 
     def decode_point(batch: int):
         """(device-timed tokens/s, ms per step, end-to-end tokens/s, ms per step, clocks)."""
-        total = args.warmup + args.steps
+        total = args.warmup + REPEATS * args.steps
         ids = prompts(batch, PROMPT)
         for _ in eng.generate(ids, total):  # builds the plan, tunes, captures; one untimed sample
             pass
@@ -326,16 +368,7 @@ def run_reference(args) -> dict:
             raise RuntimeError("the reference gave up on its own engine and fell back to Transformers")
         sampler = ClockSampler()
         sampler.start()
-        it = eng.generate(ids, total)
-        for _ in range(args.warmup):
-            next(it)
-        torch.cuda.synchronize()
-        t_start = time.perf_counter()
-        n = 0
-        for _ in it:
-            n += 1
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t_start) * 1000.0 / max(n, 1)
+        e2e_ms, _ = timed_regions(eng.generate(ids, total), args.warmup, args.steps)
         # device-timed: the reference's captured decode step, replayed back to back
         plan = eng.plans[(batch, PROMPT)]
         plan.plan.ids.copy_(torch.tensor(ids, dtype=torch.int64))
@@ -344,9 +377,6 @@ def run_reference(args) -> dict:
             plan._step_decode()
         times = []
         for _ in range(REPEATS):
-            plan._step_prefill()
-            for _ in range(args.warmup):
-                plan._step_decode()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             for _ in range(args.steps):
@@ -360,7 +390,7 @@ def run_reference(args) -> dict:
 
     try:
         value, ms_step, e2e_value, e2e_ms, clocks = decode_point(8)
-        mean_ctx = PROMPT + args.warmup + (args.steps + 1) / 2
+        mean_ctx = PROMPT + args.warmup + (args.steps * REPEATS + 1) / 2
         step_bytes = numbers["weight_bytes"] + 8 * mean_ctx * numbers["kv_bytes_per_token"]
         achieved = step_bytes / (ms_step * 1e-3) / 1e9
         points, e2e_points, point_clocks = {}, {}, {}

@@ -96,6 +96,7 @@ class SequenceCache:
         self.width = max(1, -(-self.max_context // PAGE))
         self.slots = FreeList(self.max_slots, "cache slot")
         self.length = [0] * self.max_slots
+        self.h2d_bytes = 0  # page-table rows (and their indices) copied to the device so far
         self._kv_groups: list[_KVGroup] = []
         self._state_groups: list[_StateGroup] = []
         self._where: list = [None] * len(needs)  # run -> (group, line) or None
@@ -164,6 +165,7 @@ class SequenceCache:
             rows = sorted(g.dirty)
             idx = torch.as_tensor(rows, dtype=torch.int64, device=self.device)
             g.table.index_copy_(0, idx, torch.from_numpy(g.table_host[rows]).to(self.device))
+            self.h2d_bytes += len(rows) * (8 + 4 * g.width)
             g.dirty.clear()
 
     def per_sequence_step_limit(self) -> int | None:

@@ -112,7 +112,10 @@ class BatchMeta:
         self.want_all = list(want_rows) == list(range(self.n_rows))
         self.slots, self.starts, self.q_lens = list(slots), list(starts), q_lens
 
+    uploaded = 0  # bytes of batch descriptions copied to the device so far, all instances together
+
     def upload(self) -> None:
+        BatchMeta.uploaded += self.total * 4
         self.buffer.copy_(self.host, non_blocking=True)
         if self.copied is not None:
             self.copied.record()
@@ -224,6 +227,10 @@ class Stepper:
         self.h2d_bytes = 0  # bytes of the last step's host-to-device copies
         self.passes = 0
         self._run_rings: dict = {}  # (sequences, depth) -> token ring of a DecodeRun, reused by later runs
+
+    def h2d_total(self) -> int:
+        """Bytes copied from the host to the device for steps so far: batch descriptions and page-table rows."""
+        return BatchMeta.uploaded + self.cache.h2d_bytes
 
     # ------------------------------------------------------------------
     def step(self, entries: list[StepEntry]) -> torch.Tensor:

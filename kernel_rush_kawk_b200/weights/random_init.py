@@ -11,10 +11,11 @@ to float32 and then to bfloat16 (the values that a written folder stores, so the
 The generator is counter-based. Element pair j of a tensor hashes the counters 2j
 and 2j + 1 with a 64-bit mixing function keyed by SHA-256(seed, name); the top 32
 bits of each hash give u1, u2 in (0, 1), and the Box-Muller transform
-sqrt(-2 ln u1) * (cos, sin)(2 pi u2) gives the pair's two normals. Logarithm, sine
-and cosine are evaluated here from their series with additions, multiplications,
-one division and one square root only, all of which IEEE 754 rounds the same way
-everywhere; a library's log or cos would differ in the last place between devices.
+sqrt(-2 ln u1) * (cos, sin)(2 pi u2) gives the pair's two normals. Logarithm, sine,
+cosine and the square root are evaluated here from their series (Heron's iteration
+for the root) with additions, multiplications and divisions only, which IEEE 754
+rounds the same way everywhere; a library's log, cos or sqrt differs in the last
+place between devices.
 """
 
 from __future__ import annotations
@@ -76,6 +77,23 @@ def _neg_two_log(a: torch.Tensor) -> torch.Tensor:
     return (ln_m + e * _LN2) * -2.0
 
 
+def _sqrt(y: torch.Tensor) -> torch.Tensor:
+    """Square root of positive float64 numbers by Heron's iteration from a fixed first guess: additions,
+    multiplications and divisions only (a library's square root was seen to differ in the last place
+    between a CPU and a GPU)."""
+    m, e = torch.frexp(y)
+    odd = (e & 1) == 1
+    m = torch.where(odd, m * 2.0, m)         # m in [1/2, 2), e even
+    e = torch.where(odd, e - 1, e)
+    g = m * 0.5 + 0.5                        # within 7 % of sqrt(m); each step squares the relative error
+    for _ in range(6):
+        g = (g + m / g) * 0.5
+    # times 2^(e/2), the power taken from a table of exact values (a pow() need not be exact)
+    half = torch.div(e, 2, rounding_mode="floor").long()
+    powers = torch.tensor([2.0 ** k for k in range(-600, 601)], dtype=torch.float64, device=y.device)
+    return g * powers[(half + 600).clamp(0, 1200)]
+
+
 def _cos_sin_turn(b: torch.Tensor):
     """cos and sin of 2 pi (b + 1/2) / 2^32 for integers b in [0, 2^32): the top two bits
     pick the quadrant, the rest an angle in (0, pi/2) whose series are summed."""
@@ -101,7 +119,7 @@ def standard_normals(n: int, key: int, device="cpu") -> torch.Tensor:
     view = out.view(pairs, 2)
     for first in range(0, pairs, chunk):
         j = torch.arange(first, min(first + chunk, pairs), dtype=torch.int64, device=device) * 2
-        radius = torch.sqrt(_neg_two_log(_hash32(j, key)))
+        radius = _sqrt(_neg_two_log(_hash32(j, key)))
         cos, sin = _cos_sin_turn(_hash32(j + 1, key))
         view[first:first + j.numel(), 0] = radius * cos
         view[first:first + j.numel(), 1] = radius * sin
