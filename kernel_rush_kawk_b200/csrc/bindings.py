@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_uint, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
 
 import torch
 
@@ -45,6 +45,7 @@ _SIGNATURES = {
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
     "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_selftest_wait_runs_out": [_P, c_int, _P],
+    "krk_streamk_linear": [_P, _P, _P, _P, c_longlong, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -98,6 +99,11 @@ class Kernels:
         self.has_skinny = hasattr(self.core, "krk_skinny_linear")
         self._partials: dict = {}
         self._select_scratch = None
+        self._streamk = (None, None)
+        self.has_streamk = hasattr(self.core, "krk_streamk_linear")
+        if self.has_streamk:
+            self.core.krk_streamk_scratch.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]
+            self.core.krk_streamk_scratch.restype = c_longlong
         self.use_tcgen05_attention = True
         self.launches = 0
 
@@ -214,6 +220,33 @@ class Kernels:
                                             self._stream()),
                  "tcgen05 gemm")
         return out
+
+    def streamk_linear(self, x, w, swiglu_rows=0, out_float32=False):
+        """y = x W^T for up to 128 rows of bfloat16 on the tcgen05 tensor cores with the weights as the wide
+        operand and the (feature tile, k-block) units dealt equally to the SMs (csrc/streamk_tcgen05.cu);
+        with ``swiglu_rows`` = I, W is [2I, K] and y the activated [M, I] product."""
+        M, K = x.shape
+        N = swiglu_rows if swiglu_rows else w.shape[0]
+        out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
+        n_counters = c_int(0)
+        floats = self.core.krk_streamk_scratch(M, N, K, int(swiglu_rows > 0), ctypes.byref(n_counters))
+        part, counters = self._streamk_scratch(int(floats), n_counters.value)
+        self._ok(self.core.krk_streamk_linear(out.data_ptr(), x.data_ptr(), w.data_ptr(), part.data_ptr(), part.numel(),
+                                              counters.data_ptr(), counters.numel(), M, N, K, int(swiglu_rows > 0),
+                                              int(out_float32), self.error.data_ptr(), self._stream()), "stream-K product")
+        return out
+
+    def _streamk_scratch(self, floats: int, n_counters: int):
+        """Scratch of the stream-K products: one buffer of partial tiles and one of per-tile counters for the
+        device, grown to the largest product seen (every product on a stream finishes with its scratch before
+        the next one touches it; the counters are zero between launches)."""
+        part, counters = self._streamk
+        if part is None or part.numel() < floats:
+            part = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+        if counters is None or counters.numel() < n_counters:
+            counters = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=self.device)
+        self._streamk = (part, counters)
+        return part, counters
 
     def _skinny(self, x, w, out_dtype, swiglu_rows=0):
         """x: a tensor or a Normed not yet computed (then the add and the norm run in
