@@ -19,6 +19,7 @@
 
 #define KRK_TRACE_OWNER  // with -DKRK_TRACE this file keeps a timeline buffer of its own
 #include "mma.cuh"
+#include "tcgen05.cuh"  // mbarriers with bounded waits and TMA tile loads, for the TMA-fed single-token kernel
 
 #ifndef KRK_HEAD_DIM
 #error "compile with -DKRK_HEAD_DIM=<head size>"
@@ -42,6 +43,15 @@ constexpr int TILE_ELEMS = KRK_PAGE * KVP;
 __device__ __forceinline__ int kv_off(int key, int piece) {
   return key * KVP + ((KV_SWIZZLE ? (piece ^ (key & 7)) : piece) << 3);
 }
+// The same page as TMA writes it with the 128-byte swizzle: D / 64 sub-tiles of [64 keys][128 bytes], piece c of
+// key k of a sub-tile at piece c ^ (k & 7). Head sizes that are multiples of 64 only.
+constexpr bool TMA_PAGES = (D % 64 == 0);
+constexpr int SUB_ELEMS = KRK_PAGE * 64;  // elements of one sub-tile (8 KB)
+template <bool TMA>
+__device__ __forceinline__ int page_off(int key, int piece) {
+  if (TMA) return (piece >> 3) * SUB_ELEMS + key * 64 + (((piece & 7) ^ (key & 7)) << 3);
+  return kv_off(key, piece);
+}
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Copy one page [64][D] of one kv head to shared memory [64][DP], all threads of the block.
@@ -54,7 +64,7 @@ __device__ __forceinline__ void load_page(bf16* dst, const bf16* __restrict__ sr
 }
 
 // S[16 x (8*NTILES)] = Q[16 x D] . K^T for keys key0 .. key0 + 8*NTILES - 1 of the tile in shared memory.
-template <int NTILES>
+template <int NTILES, bool TMA = false>
 __device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&qf)[KSTEPS][4], const bf16* ks, int key0,
                                         int lane) {
   // even and odd k-steps accumulate apart and are added at the end: two chains of KSTEPS / 2 dependent MMAs
@@ -69,7 +79,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&
 #pragma unroll
     for (int n = 0; n < NTILES; n += 2) {
       uint32_t b0, b1, b2, b3;
-      const bf16* p = ks + kv_off(key0 + n * 8 + ((lane >> 4) << 3) + (lane & 7), kk * 2 + ((lane >> 3) & 1));
+      const bf16* p = ks + page_off<TMA>(key0 + n * 8 + ((lane >> 4) << 3) + (lane & 7), kk * 2 + ((lane >> 3) & 1));
       ldmatrix_x4(b0, b1, b2, b3, p);
       if (kk & 1) {
         mma_bf16_16816(odd[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
@@ -87,7 +97,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NTILES][4], const uint32_t (&
 }
 
 // O[16 x D] += P[16 x (8*NTILES)] . V for the same keys; p holds probabilities (float) in S's layout.
-template <int NTILES>
+template <int NTILES, bool TMA = false>
 __device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[NTILES][4], const bf16* vs, int key0,
                                         int lane) {
 #pragma unroll
@@ -99,7 +109,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[
 #pragma unroll
     for (int n = 0; n < DTILES; n += 2) {
       uint32_t b0, b1, b2, b3;
-      const bf16* q = vs + kv_off(key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n + (lane >> 4));
+      const bf16* q = vs + page_off<TMA>(key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n + (lane >> 4));
       ldmatrix_x4_trans(b0, b1, b2, b3, q);
       mma_bf16_16816(o[n], a0, a1, a2, a3, b0, b1);
       mma_bf16_16816(o[n + 1], a0, a1, a2, a3, b2, b3);
@@ -784,6 +794,267 @@ int launch_decode_fused(bf16* out, const bf16* qkv, int q_stride, int HQ, int HK
                                  n_pos, inbox_rows, error);
 }
 
+
+#if KRK_HEAD_DIM % 64 == 0
+// ---------------------------------------------------------------------------------
+// The same single-token step for many sequences (one block walks all keys of its
+// (sequence, kv head); no cluster), fed by TMA. A fifth warp is the producer: one
+// thread requests pages as tiled bulk copies (128-byte swizzle, so ldmatrix stays free
+// of bank conflicts) into a ring of units, a unit being one page of keys or one of
+// values; each unit completes on an mbarrier of its own and is handed back on another
+// as soon as the four consumer warps have read it, keys before values. With units of
+// half a page-pair, all but one unit of the ring are in flight while one is computed
+// on (five of six at head size 128, against two of three page-pairs with cp.async),
+// and no consumer thread spends instructions on copying. A request under load takes
+// some microseconds to arrive, so bytes in flight per SM are what bounds this kernel.
+// ---------------------------------------------------------------------------------
+constexpr int UNIT_ELEMS = KRK_PAGE * D;  // one page of keys (or of values) of one kv head
+constexpr uint32_t UNIT_BYTES = UNIT_ELEMS * 2;
+constexpr int TMA_THREADS = 160;          // four consumer warps and the producer warp
+constexpr int TMA_MAX_WIDTH = 1024;       // page-table entries of a sequence that the block keeps in shared memory
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
+                            const void* __restrict__ q_gain, const void* __restrict__ k_gain, int gain_f32,
+                            const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t, float eps,
+                            const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                            const int* __restrict__ table, int width, bf16* __restrict__ k_cache,
+                            bf16* __restrict__ v_cache, float scale_log2, int window, int row_tiles, int n_pos, int ring,
+                            int* __restrict__ error) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  bf16* units = reinterpret_cast<bf16*>(base);                                // [ring][UNIT_ELEMS], later the partials
+  bf16* q_s = reinterpret_cast<bf16*>(base + (size_t)ring * UNIT_BYTES);      // [16][DP] rotated queries
+  bf16* kv_new = q_s + 16 * DP;                                               // [2][D] the new token's key and value
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(kv_new + 2 * D);           // [ring]
+  uint64_t* empty_bar = full_bar + ring;                                      // [ring]
+  int* pages = reinterpret_cast<int*>(empty_bar + ring);                      // [key blocks of this sequence]
+
+  grid_launch_dependents();
+  const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
+  const int seq = blockIdx.z;
+  const int G = HQ / HKV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  // read before the wait on the previous kernel, as in the cluster kernel: positions, slots, the page table
+  int pos = __ldcg(seq_start + seq);
+  const int slot = __ldcg(seq_slot + seq);
+  if (pos < 0 || pos >= n_pos) {
+    if (threadIdx.x == 0 && error) atomicExch(error, 2);
+    pos = max(0, min(pos, n_pos - 1));
+  }
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
+  const int n_blocks = j_last - j_first + 1;
+  const int n_units = 2 * n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < ring; ++r) {
+      tc::mbar_init(full_bar + r, 1);
+      tc::mbar_init(empty_bar + r, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ---- producer ----
+    for (int i = lane; i < n_blocks; i += 32) pages[i] = table[(size_t)slot * width + (j_first + i) % width];
+    __syncwarp();
+    if (lane == 0) {
+      for (int u = 0; u < n_units; ++u) {
+        const int r = u % ring;
+        if (u >= ring && !tc::mbar_wait(empty_bar + r, (uint32_t)((u / ring) - 1) & 1)) {
+          if (error) atomicExch(error, 19);
+          break;
+        }
+        tc::mbar_expect_tx(full_bar + r, UNIT_BYTES);
+        const int row = (pages[u >> 1] * HKV + kh) * KRK_PAGE;
+        const CUtensorMap* map = (u & 1) ? &map_v : &map_k;
+        bf16* dst = units + (size_t)r * UNIT_ELEMS;
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) tc::tma_load_2d(dst + h * SUB_ELEMS, map, full_bar + r, h * 64, row);
+      }
+    }
+    return;
+  }
+
+  // ---- consumers: warps 0..3 ----
+  grid_dependency_wait();
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+  const size_t head_off = (size_t)kh * KRK_PAGE * D;
+  const bf16* row = qkv + (size_t)seq * q_stride;
+  const int q_rows = min(16, G - rt * 16);
+  const int k_warp = q_rows % 4;
+  constexpr int MAX_ROWS = 4;
+  HeadRow regs[MAX_ROWS];
+  HeadRow k_regs;
+  float v_regs[(D + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i) {
+    const int r = warp + 4 * i;
+    if (r < q_rows) regs[i].load_values(row + (size_t)(kh * G + rt * 16 + r) * D, q_gain, gain_f32, lane);
+  }
+  if (warp == k_warp) {
+    k_regs.load_values(row + (size_t)(HQ + kh) * D, k_gain, gain_f32, lane);
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      v_regs[i] = d < D ? __bfloat162float(row[(size_t)(HQ + HKV + kh) * D + d]) : 0.f;
+    }
+  }
+  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
+  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i)
+    if (warp + 4 * i < q_rows) regs[i].load_angles(cos_row, sin_row, lane);
+  if (warp == k_warp) k_regs.load_angles(cos_row, sin_row, lane);
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i) {
+    const int r = warp + 4 * i;
+    if (r < q_rows) {
+      regs[i].finish(q_s + r * DP, q_gain != nullptr, cos_t != nullptr, eps, lane);
+    } else if (r < 16) {
+      for (int d = lane; d < D; d += 32) q_s[r * DP + d] = __float2bfloat16_rn(0.f);
+    }
+  }
+  if (warp == k_warp) {
+    k_regs.finish(kv_new, k_gain != nullptr, cos_t != nullptr, eps, lane);
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) kv_new[D + d] = __float2bfloat16_rn(v_regs[i]);
+    }
+    __syncwarp();
+    if (rt == 0) {
+      const int page = table[(size_t)slot * width + j_last % width];
+      const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
+      for (int d = lane; d < D; d += 32) {
+        k_cache[at + d] = kv_new[d];
+        v_cache[at + d] = kv_new[D + d];
+      }
+    }
+  }
+  consumer_sync();
+
+  uint32_t qf[KSTEPS][4];
+  load_q(qf, q_s + g * DP, q_s + (g + 8) * DP, lane);
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  bool alive = true;  // false once a wait ran out: the flow stays the same for all warps, the results are void
+  auto arrived = [&](int u) {
+    if (alive && !tc::mbar_wait(full_bar + u % ring, (uint32_t)(u / ring) & 1)) {
+      alive = false;
+      if (lane == 0 && error) atomicExch(error, 19);
+    }
+  };
+  auto hand_back = [&](int u) {
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(empty_bar + u % ring);
+  };
+  const int tid = threadIdx.x;  // 0..127 among the consumers
+  for (int j = j_first; j <= j_last; ++j) {
+    const int uk = 2 * (j - j_first), uv = uk + 1;
+    bf16* ks = units + (size_t)(uk % ring) * UNIT_ELEMS;
+    bf16* vs = units + (size_t)(uv % ring) * UNIT_ELEMS;
+    arrived(uk);
+    if (j == j_last) {  // the page in shared memory predates this step's write: put the new key in
+      for (int i = tid; i < D; i += 128) ks[page_off<true>(pos % KRK_PAGE, i >> 3) + (i & 7)] = kv_new[i];
+      consumer_sync();
+    }
+    const int key0 = warp * 16;
+    float s[2][4];
+    qk_tile<2, true>(s, qf, ks, key0, lane);
+    hand_back(uk);
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = j * KRK_PAGE + key0 + n * 8 + 2 * t4 + (c & 1);
+        s[n][c] = (key <= pos && key >= lo) ? s[n][c] * scale_log2 : -INFINITY;
+      }
+    softmax_update<2>(s, m, l, o);
+    arrived(uv);
+    if (j == j_last) {
+      for (int i = tid; i < D; i += 128) vs[page_off<true>(pos % KRK_PAGE, i >> 3) + (i & 7)] = kv_new[D + i];
+      consumer_sync();
+    }
+    pv_tile<2, true>(o, s, vs, key0, lane);
+    hand_back(uv);
+  }
+  consumer_sync();  // every warp is done with the ring: it now holds the warps' partials
+
+  constexpr int RP = D + 2;
+  float* red = reinterpret_cast<float*>(base);  // [4 warps][16 rows][RP]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float* dst = red + ((size_t)warp * 16 + g + 8 * h) * RP;
+    if (t4 == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n) {
+      dst[n * 8 + 2 * t4] = o[n][2 * h];
+      dst[n * 8 + 2 * t4 + 1] = o[n][2 * h + 1];
+    }
+  }
+  consumer_sync();
+  for (int r = warp; r < q_rows; r += 4) {  // the four warps' partials of a row, in warp order
+    float mw[4], big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { mw[w] = red[((size_t)w * 16 + r) * RP + D]; big = fmaxf(big, mw[w]); }
+    const float safe = big == -INFINITY ? 0.f : big;
+    float wgt[4], lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
+    const float inv = 1.0f / lsum;
+    bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
+    for (int d = lane; d < D; d += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+      dst[d] = __float2bfloat16_rn(acc * inv);
+    }
+  }
+}
+
+int launch_decode_tma(bf16* out, const bf16* qkv, int q_stride, int HQ, int HKV, const void* q_gain, const void* k_gain,
+                      int gain_f32, const bf16* cos_t, const bf16* sin_t, float eps, const int* seq_slot,
+                      const int* seq_start, const int* table, int width, bf16* k_cache, bf16* v_cache, int n_pages,
+                      int n_seqs, float scale, int window, int n_pos, int* error, cudaStream_t stream) {
+  if (width > TMA_MAX_WIDTH) return -2;
+  const int G = HQ / HKV;
+  const int row_tiles = (G + 15) / 16;
+  const size_t fixed = 1024 + (size_t)(16 * DP + 2 * D) * sizeof(bf16) + (size_t)width * sizeof(int) + 64;
+  // two blocks per SM: the ring takes what half of an SM's shared memory leaves
+  int ring = (int)((111 * 1024 - fixed) / UNIT_BYTES);
+  ring = ring > 12 ? 12 : ring;
+  if (ring < 2 || (size_t)ring * UNIT_BYTES < (size_t)4 * 16 * (D + 2) * sizeof(float)) return -2;
+  const size_t smem = fixed + (size_t)ring * UNIT_BYTES + (size_t)2 * ring * 8;
+  CUtensorMap map_k, map_v;
+  const long long rows = (long long)n_pages * HKV * KRK_PAGE;
+  int rc = tc::make_map_bf16(&map_k, k_cache, rows, D, D, 64);
+  if (rc) return rc;
+  rc = tc::make_map_bf16(&map_v, v_cache, rows, D, D, 64);
+  if (rc) return rc;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  return (int)launch_pdl(attention_decode_tma_kernel, dim3(1, HKV * row_tiles, n_seqs), dim3(TMA_THREADS), smem, stream,
+                         map_k, map_v, out, qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, cos_t, sin_t, eps, seq_slot,
+                         seq_start, table, width, k_cache, v_cache, scale * LOG2E, window, row_tiles, n_pos, ring, error);
+}
+#endif  // head sizes that TMA pages serve
+
 }  // namespace
 
 // out [rows, HQ*D]; q rows are the first HQ*D elements of each qkv row (row stride q_stride elements).
@@ -867,6 +1138,27 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
   return launch_decode_fused<2>((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32,
                                 (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot, seq_start, table, width,
                                 (bf16*)k_cache, (bf16*)v_cache, n_seqs, scale, window, splits, n_pos, error, stream);
+}
+
+// The same step with one block per (sequence, kv head) fed by TMA (see attention_decode_tma_kernel): for many
+// sequences, where no key split is wanted. n_pages: pages of the cache (for the TMA maps). Returns -2 for head
+// sizes that are no multiple of 64 or page tables wider than 1024 entries: the caller then takes the kernel above.
+KRK_API int krk_attention_decode_fused_tma(void* out, const void* qkv, int q_stride, int HQ, int HKV, const void* q_gain,
+                                           const void* k_gain, int gain_f32, const void* cos_t, const void* sin_t,
+                                           float eps, const int* seq_slot, const int* seq_start, const int* table,
+                                           int width, void* k_cache, void* v_cache, int n_pages, int n_seqs, float scale,
+                                           int window, int n_pos, int* error, cudaStream_t stream) {
+#if KRK_HEAD_DIM % 64 == 0
+  if (n_seqs == 0) return 0;
+  const int G = HQ / HKV;
+  const int row_tiles = (G + 15) / 16;
+  if (HKV * row_tiles > 65535 || n_seqs > 65535) return -3;
+  return launch_decode_tma((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, (const bf16*)cos_t,
+                           (const bf16*)sin_t, eps, seq_slot, seq_start, table, width, (bf16*)k_cache, (bf16*)v_cache,
+                           n_pages, n_seqs, scale, window, n_pos, error, stream);
+#else
+  return -2;
+#endif
 }
 
 #endif  // head size served by the tensor-core kernels

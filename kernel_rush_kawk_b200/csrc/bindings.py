@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
+from ctypes import c_float, c_int, c_uint, c_void_p
 
 import torch
 
@@ -45,7 +45,6 @@ _SIGNATURES = {
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
     "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_selftest_wait_runs_out": [_P, c_int, _P],
-    "krk_streamk_linear": [_P, _P, _P, _P, c_longlong, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
 }
 _ATTN_SIGNATURES = {
@@ -59,6 +58,8 @@ _ATTN_SIGNATURES = {
                                       c_int, c_float, c_int, _P, _P],
     "krk_attention_decode_fused": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
                                    _P, c_int, c_float, c_int, c_int, c_int, _P, _P],
+    "krk_attention_decode_fused_tma": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
+                                       _P, c_int, c_int, c_float, c_int, c_int, _P, _P],
 }
 
 
@@ -99,12 +100,8 @@ class Kernels:
         self.has_skinny = hasattr(self.core, "krk_skinny_linear")
         self._partials: dict = {}
         self._select_scratch = None
-        self._streamk = (None, None)
-        self.has_streamk = hasattr(self.core, "krk_streamk_linear")
-        if self.has_streamk:
-            self.core.krk_streamk_scratch.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]
-            self.core.krk_streamk_scratch.restype = c_longlong
         self.use_tcgen05_attention = True
+        self.use_tma_decode_attention = True
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -221,33 +218,6 @@ class Kernels:
                  "tcgen05 gemm")
         return out
 
-    def streamk_linear(self, x, w, swiglu_rows=0, out_float32=False):
-        """y = x W^T for up to 128 rows of bfloat16 on the tcgen05 tensor cores with the weights as the wide
-        operand and the (feature tile, k-block) units dealt equally to the SMs (csrc/streamk_tcgen05.cu);
-        with ``swiglu_rows`` = I, W is [2I, K] and y the activated [M, I] product."""
-        M, K = x.shape
-        N = swiglu_rows if swiglu_rows else w.shape[0]
-        out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
-        n_counters = c_int(0)
-        floats = self.core.krk_streamk_scratch(M, N, K, int(swiglu_rows > 0), ctypes.byref(n_counters))
-        part, counters = self._streamk_scratch(int(floats), n_counters.value)
-        self._ok(self.core.krk_streamk_linear(out.data_ptr(), x.data_ptr(), w.data_ptr(), part.data_ptr(), part.numel(),
-                                              counters.data_ptr(), counters.numel(), M, N, K, int(swiglu_rows > 0),
-                                              int(out_float32), self.error.data_ptr(), self._stream()), "stream-K product")
-        return out
-
-    def _streamk_scratch(self, floats: int, n_counters: int):
-        """Scratch of the stream-K products: one buffer of partial tiles and one of per-tile counters for the
-        device, grown to the largest product seen (every product on a stream finishes with its scratch before
-        the next one touches it; the counters are zero between launches)."""
-        part, counters = self._streamk
-        if part is None or part.numel() < floats:
-            part = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
-        if counters is None or counters.numel() < n_counters:
-            counters = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=self.device)
-        self._streamk = (part, counters)
-        return part, counters
-
     def _skinny(self, x, w, out_dtype, swiglu_rows=0):
         """x: a tensor or a Normed not yet computed (then the add and the norm run in
         the kernel's prologue)."""
@@ -340,6 +310,16 @@ class Kernels:
             splits = 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 192 else 1
             gain = q_gain if q_gain is not None else k_gain
             n_pos = cos.shape[0] if cos is not None else 0x7fffffff
+            if (splits == 1 and self.use_tma_decode_attention and head_dim % 64 == 0 and cache.width <= 1024
+                    and hasattr(lib, "krk_attention_decode_fused_tma")):
+                # many sequences: one block per (sequence, kv head), pages by TMA into a ring of half page-pairs
+                self._ok(lib.krk_attention_decode_fused_tma(
+                    out.data_ptr(), qkv.data_ptr(), qkv.stride(0), heads, cache.kv_heads, _ptr(q_gain), _ptr(k_gain),
+                    int(gain is not None and gain.dtype == torch.float32), _ptr(cos), _ptr(sin), eps,
+                    batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
+                    cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], n, scale, int(window or 0), n_pos,
+                    self.error.data_ptr(), self._stream()), "fused decode attention (TMA)")
+                return out
             self._ok(lib.krk_attention_decode_fused(
                 out.data_ptr(), qkv.data_ptr(), qkv.stride(0), heads, cache.kv_heads, _ptr(q_gain), _ptr(k_gain),
                 int(gain is not None and gain.dtype == torch.float32), _ptr(cos), _ptr(sin), eps,

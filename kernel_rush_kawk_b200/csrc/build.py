@@ -26,8 +26,7 @@ from pathlib import Path
 
 SRC_DIR = Path(__file__).parent
 
-CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu",
-                "streamk_tcgen05.cu"]
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu"]
 ATTN_SOURCES = ["attention_simple.cu", "attention_mma.cu", "attention_tcgen05.cu"]
 HEADERS = ["common.cuh", "mma.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 

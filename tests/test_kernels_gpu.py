@@ -287,11 +287,12 @@ def test_a_position_outside_the_rotary_table_is_flagged(ops, rows):
 
 @pytest.mark.parametrize("shape", ATTN_SHAPES + [(40, 2, 64)])
 @pytest.mark.parametrize("window", [None, 70])
-@pytest.mark.parametrize("n_seqs", [1, 3, 40])
+@pytest.mark.parametrize("n_seqs", [1, 3, 40, 100])
 def test_fused_decode_attention_against_the_two_kernel_path(ops, shape, window, n_seqs):
     """Single-token steps in bfloat16: norm + rotation + cache write + attention + merge in
     one launch, against the plain reference of each stage; 1, 3 and 40 sequences give
-    cluster sizes 8, 4 or 2, and 1."""
+    cluster sizes 8, 4 or 2, and 1; with one block per (sequence, kv head, row tile), head
+    sizes 64 and 128 take the TMA-fed kernel (at 100 sequences also the shape with two row tiles)."""
     heads, kv_heads, D = shape
     dtype = torch.bfloat16
     ref = TorchOps(dtype)
@@ -318,6 +319,42 @@ def test_fused_decode_attention_against_the_two_kernel_path(ops, shape, window, 
     close(cache.k, ref_cache.k, dtype, "key pages after the fused step")
     assert torch.equal(cache.v, ref_cache.v)
     close(got, want, dtype, f"fused decode attention {shape} window {window} seqs {n_seqs}")
+
+
+@pytest.mark.parametrize("shape", [(8, 8, 64), (32, 8, 128), (40, 2, 64), (4, 4, 256)])
+@pytest.mark.parametrize("window", [None, 150])
+def test_tma_fed_decode_attention_equals_the_cp_async_kernel(ops, shape, window):
+    """Many sequences, long ones among them (18 pages through a ring of 6 or 12 units, so every unit is
+    reused), a page table that wraps under the window: the TMA-fed kernel and the cp.async kernel walk
+    the keys in the same order and must agree to the bit, cache pages included."""
+    heads, kv_heads, D = shape
+    dtype = torch.bfloat16
+    n_seqs, width = 120, 18
+    rnd = random.Random(9)
+    starts = [rnd.choice([0, 5, 63, 64, 65, 500, 1000, 1151]) for _ in range(n_seqs)]
+    slots = list(range(n_seqs))
+    rnd.shuffle(slots)
+    batch = make_batch(slots, starts, [1] * n_seqs)
+    qg = (1.5 + 0.1 * rand((D,), torch.float32, 81)).to(dtype)
+    kg = (1.5 + 0.1 * rand((D,), torch.float32, 82)).to(dtype)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    scale = 1.0 / math.sqrt(D)
+    results = []
+    for use_tma in (True, False):
+        cache = make_cache(n_seqs * width + 3, kv_heads, D, n_seqs, width, dtype, 80)
+        cache.window = window
+        qkv = rand((n_seqs, (heads + 2 * kv_heads) * D), dtype, 83)
+        ops.use_tma_decode_attention = use_tma
+        try:
+            out = ops.rope_attention(qkv, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, cache, scale, window)
+        finally:
+            ops.use_tma_decode_attention = True
+        results.append((out, cache.k, cache.v))
+    ops.check()
+    for a, b, what in zip(results[0], results[1], ("output", "key pages", "value pages")):
+        assert torch.equal(a, b), f"{what} differ between the TMA-fed and the cp.async kernel"
 
 
 @pytest.mark.parametrize("shape", [(8, 2, 64), (32, 8, 128), (6, 2, 128), (5, 1, 64)])
