@@ -21,6 +21,11 @@ at batch 1 and 64 (``points``); a 2,048-token prompt is prefilled (``prefill``).
   against the measured copy bandwidth.
 * ``prefill.frac``: the step's flops over its time over the measured bfloat16 peak.
 
+``--only workload_8b`` and ``--only workload_14b`` run the baseline's two larger
+configurations (Qwen3-8B sizes: 8 prompts of 256 to 2,048 tokens, 128 greedy steps;
+Qwen3-14B sizes: 16 prompts of 512 to 4,096 tokens, 128 steps at temperature 0.7)
+through ``Engine.generate`` and print a short line of their own.
+
 With --gpus above 1 it says that it runs on one GPU only and exits with 2.
 --impl reference runs the unmodified reference from baseline/_ref (a copy of its
 source tree: it is source-only, with no setup.py or pyproject.toml to install) on
@@ -144,6 +149,40 @@ def model_numbers(cfg, layers: int) -> dict:
     kv_bytes_per_token = 2 * 2 * layers * HKV * D
     return {"per_layer": per_layer, "weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token,
             "head": head, "attn_dim": HQ * D}
+
+
+WORKLOADS = {
+    # the two larger configurations of the baseline: (preset, prompts, shortest, longest, steps, temperature, context)
+    "workload_8b": ("qwen3_8b", 8, 256, 2048, 128, 0.0, 4096),
+    "workload_14b": ("qwen3_14b", 16, 512, 4096, 128, 0.7, 8192),
+}
+
+
+def run_workload(args) -> dict:
+    """One of the baseline's larger configurations end to end through ``Engine.generate``: an unequal batch
+    of seeded prompts, then decode steps (greedy at the 8B sizes, temperature 0.7 at the 14B sizes), timed by
+    the engine's own per-call statistics (host clock). Run twice; the second run is reported."""
+    import torch
+
+    from kernel_rush_kawk_b200 import Engine, Qwen3Config
+
+    preset, n, shortest, longest, steps, temperature, context = WORKLOADS[args.only]
+    base = Qwen3Config.preset(preset)
+    layers = args.layers or base.num_hidden_layers
+    cfg = Qwen3Config.from_dict({**base.to_dict(), "num_hidden_layers": layers})
+    engine = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_slots=n, max_context=context,
+                                max_tokens=n * context)
+    gen = torch.Generator().manual_seed(4321)
+    lengths = torch.randint(shortest, longest + 1, (n,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (k,), generator=gen).tolist() for k in lengths]
+    for _ in range(2):
+        produced = sum(1 for _ in engine.generate(prompts, steps, temperature=temperature, seed=7))
+        torch.cuda.synchronize()
+    st = engine.last_stats
+    return {"only": args.only, "model": preset, "layers": layers, "layers_of_model": base.num_hidden_layers,
+            "prompts": n, "prompt_tokens": st.prompt_tokens, "steps": produced, "temperature": temperature,
+            "prefill_ms": round(st.prefill_ms, 2), "prefill_tokens_per_s": round(st.prefill_tokens_per_s, 1),
+            "decode_ms_per_step": round(st.decode_ms_per_step, 4), "decode_tokens_per_s": round(st.decode_tokens_per_s, 1)}
 
 
 def run_ours(args) -> dict:
@@ -450,8 +489,9 @@ def main() -> int:
     p.add_argument("--steps", type=int, default=256)
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64"],
-                   help="run one piece only (for profiling)")
+    p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64",
+                                                  "workload_8b", "workload_14b"],
+                   help="run one piece only (for profiling), or one of the baseline's larger configurations end to end")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()
     if args.impl == "reference":
@@ -462,7 +502,7 @@ def main() -> int:
         print(f"bench.py runs on one GPU only (this library has no multi-GPU path); got --gpus {args.gpus}")
         return 2
     args.warmup = max(args.warmup, 3)
-    print(json.dumps(run_ours(args)))
+    print(json.dumps(run_workload(args) if args.only in WORKLOADS else run_ours(args)))
     return 0
 
 
