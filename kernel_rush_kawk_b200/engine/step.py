@@ -16,7 +16,9 @@ A step that is too large for one pass (more rows than ``max_step_rows``, or more
 tokens of one sequence than a window group's ring allows) is cut into passes;
 since a pass may start anywhere in a sequence, the cut changes nothing but
 rounding. A step in which every sequence brings one token runs from a captured
-CUDA graph when the model's parts allow it.
+CUDA graph when the model's parts allow it. The tensor such a step returns is the
+captured step's own output buffer: the next single-token step of the same batch
+size overwrites it, so a caller that keeps logits across steps copies them.
 """
 
 from __future__ import annotations

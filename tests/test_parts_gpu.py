@@ -191,11 +191,14 @@ def register_toy():
     class DecayMixer(Mixer):
         """s_t = decay * s_{t-1} + h_t (state [hidden] per sequence, float32); out_t = s_t W^T."""
 
-        graph_safe = False  # reads the step's host-side lengths
-
         def __init__(self, params):
             super().__init__(params)
             self.hidden, self.decay = int(params["hidden"]), float(params["decay"])
+            # A step of several tokens scans them in order and reads the step's lengths on the host. With
+            # "on_device" a single-token step touches device arrays only, so it can be captured and queued
+            # ahead of the host; without it the part declares that its steps cannot be.
+            self.on_device = bool(params.get("on_device", False))
+            self.graph_safe = self.on_device
 
         def tensor_specs(self):
             return {"mix": TensorSpec((self.hidden, self.hidden))}
@@ -208,6 +211,11 @@ def register_toy():
 
         def forward(self, ctx, h, cache):
             rows = h.tensor().float()
+            if self.on_device and ctx.batch.is_decode:  # one token each: row r belongs to sequence r
+                slots = ctx.batch.seq_slot.long()
+                s = cache.state[slots] * self.decay + rows
+                cache.state.index_copy_(0, slots, s)
+                return (s.to(self.w.dtype).float() @ self.w.float().t()).to(self.w.dtype)
             out = torch.empty_like(rows)
             r = 0
             for slot, n in zip(ctx.batch.slots, ctx.batch.q_lens):
@@ -225,14 +233,16 @@ def register_toy():
     class ToyConfig(ModelConfig):
         hidden: int = 48
         vocab: int = 97
+        state_on_device: bool = False
         architecture = "ToyDecoderForTests"
 
         @classmethod
         def from_dict(cls, raw):
-            return cls(raw.get("hidden", 48), raw.get("vocab", 97))
+            return cls(raw.get("hidden", 48), raw.get("vocab", 97), bool(raw.get("state_on_device", False)))
 
         def to_dict(self):
-            return {"architectures": [self.architecture], "hidden": self.hidden, "vocab": self.vocab}
+            return {"architectures": [self.architecture], "hidden": self.hidden, "vocab": self.vocab,
+                    "state_on_device": self.state_on_device}
 
         @classmethod
         def preset_names(cls):
@@ -253,7 +263,8 @@ def register_toy():
             {k: f"l{i}.attn.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
         layers = [
             LayerSpec("prenorm", norm("l0.n1"), attn(0, True), norm("l0.n2"), ffn(0)),
-            LayerSpec("prenorm", norm("l1.n1"), PartSpec("test_decay", {"hidden": H, "decay": 0.5}, {"mix": "l1.mix"}),
+            LayerSpec("prenorm", norm("l1.n1"), PartSpec("test_decay", {"hidden": H, "decay": 0.5,
+                                                                      "on_device": cfg.state_on_device}, {"mix": "l1.mix"}),
                       norm("l1.n2"), ffn(1)),
             LayerSpec("prenorm", norm("l2.n1"), attn(2, False), norm("l2.n2"), ffn(2)),
         ]
@@ -352,6 +363,48 @@ def test_toy_architecture_with_a_state_mixer_a_repeated_layer_and_a_shared_cache
     assert preset_config("toy_small").vocab == 61
     small = Engine.from_random("toy_small", seed=1, std=0.08, dtype=NAME[dtype], max_slots=2)
     assert small.plan.vocab_size == 61 and len(list(small.generate([[1, 2, 3]], 2))) == 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_state_mixer_whose_single_token_steps_stay_on_the_device_is_captured_and_runs_ahead(dtype, tmp_path):
+    """The same toy architecture with its state mixer's single-token path on device arrays only: the model
+    is then safe to capture, its steps replay from a graph and the generation loop queues them ahead of
+    the host. Logits equal the plain implementation's, and generation equals that of the engine whose
+    steps go through the host one by one."""
+    import dataclasses
+
+    from kernel_rush_kawk_b200 import Engine, StepEntry, write_model_folder
+    from safetensors.torch import load_file
+
+    cfg = dataclasses.replace(register_toy(), state_on_device=True)
+    folder = write_model_folder(tmp_path / "toy_dev", cfg, 5, std=0.08, gain_std=0.1)
+    engine = Engine(folder, dtype=NAME[dtype], max_tokens=1024, max_slots=4)
+    assert engine.model.graph_safe and engine.stepper.use_graphs
+    w = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (70, 9)]
+    refs = [toy_plain(w, s, None if dtype == torch.float32 else torch.bfloat16) for s in seqs]
+    cuts = [40, 3]
+    slots = [engine.cache.alloc() for _ in seqs]
+    got = [[] for _ in seqs]
+    out = engine.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cuts)])
+    got[0].append(out[:cuts[0]]); got[1].append(out[cuts[0]:])
+    fed = list(cuts)
+    while any(f < len(s) for f, s in zip(fed, seqs)):
+        live = [i for i in range(2) if fed[i] < len(seqs[i])]
+        out = engine.step([StepEntry(slots[i], [seqs[i][fed[i]]], [0]) for i in live])
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1].clone()); fed[i] += 1
+    for i in range(2):
+        assert_close(torch.cat(got[i]), refs[i], NAME[dtype], f"toy model with device state, request {i}")
+    for s in slots:
+        engine.cache.free(s)
+    assert engine.stepper._graphs, "single-token steps were captured"
+    prompts = [seqs[0][:20], seqs[1]]
+    ahead = list(engine.generate(prompts, 9))
+    by_host = list(Engine(folder, dtype=NAME[dtype], max_tokens=1024, max_slots=4, use_cuda_graphs=False).generate(prompts, 9))
+    assert ahead == by_host
+    engine.cache.check()
 
 
 # ---------------------------------------------------------------------------------
