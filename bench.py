@@ -52,6 +52,7 @@ PROMPT = 1024
 PREFILL_TOKENS = 2048
 SLOTS, CONTEXT = 64, 4096
 REPEATS = 5  # timed regions per decode point; the median is reported
+PREFILL_REPEATS = 15  # timed prefills (a quarter of a second: long enough for the clock sampler); the median is reported
 
 
 def peaks() -> dict:
@@ -80,7 +81,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -296,7 +297,7 @@ def run_ours(args) -> dict:
     times = []
     sampler = ClockSampler()
     sampler.start()
-    for i in range(args.warmup + 5):
+    for i in range(args.warmup + PREFILL_REPEATS):
         slot = cache.alloc()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -445,7 +446,7 @@ def run_reference(args) -> dict:
         sampler = ClockSampler()
         sampler.start()
         times = []
-        for i in range(args.warmup + 5):
+        for i in range(args.warmup + PREFILL_REPEATS):
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             plan._step_prefill()

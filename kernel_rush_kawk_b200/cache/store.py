@@ -168,6 +168,16 @@ class SequenceCache:
             self.h2d_bytes += len(rows) * (8 + 4 * g.width)
             g.dirty.clear()
 
+    def save_state(self, slots) -> list:
+        """Copies of the fixed-size state that these slots hold, one tensor per state group."""
+        idx = torch.as_tensor(list(slots), dtype=torch.int64, device=self.device)
+        return [g.state.index_select(1, idx) for g in self._state_groups]
+
+    def restore_state(self, slots, saved: list) -> None:
+        idx = torch.as_tensor(list(slots), dtype=torch.int64, device=self.device)
+        for g, s in zip(self._state_groups, saved):
+            g.state.index_copy_(1, idx, s)
+
     def per_sequence_step_limit(self) -> int | None:
         """The most tokens one sequence may bring in one pass, or None if any number will do. A group that
         keeps a window of keys cycles through a ring of pages sized for ``step_tokens`` new positions;

@@ -405,13 +405,17 @@ class Stepper:
         meta.fill(slots, starts, token_lists, list(range(n)))
         ctx = StepContext(self.ops, meta, self.cache)
         # Run once outside a capture: everything that allocates or initialises lazily
-        # does so now. The pass writes this step's keys and values; the captured run
-        # below writes the same values to the same places again.
+        # does so now. The pass writes this step's keys and values; the replay of the
+        # captured step writes the same values to the same places again. Fixed-size
+        # state is not like that (a second update is a different state), so the
+        # sequences' state is put back as it was before the trial run.
+        saved = self.cache.save_state(slots)
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
             self.model.forward(ctx, meta.want)
         torch.cuda.current_stream(self.device).wait_stream(side)
+        self.cache.restore_state(slots, saved)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.ops, "launches", 0)
