@@ -357,6 +357,34 @@ def test_tma_fed_decode_attention_equals_the_cp_async_kernel(ops, shape, window)
         assert torch.equal(a, b), f"{what} differ between the TMA-fed and the cp.async kernel"
 
 
+@pytest.mark.parametrize("shape", [(8, 8, 64), (32, 8, 128)])
+def test_tma_fed_decode_attention_round_a_wrapped_ring_of_pages(ops, shape):
+    """A window of 150 keys in a ring of 6 pages, sequences thousands of tokens long: the positions' pages
+    are table entries modulo the ring, and the kernel's own ring of units turns several times per block.
+    Against the plain attention over the same pages."""
+    heads, kv_heads, D = shape
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    n_seqs, width, window = 110, 6, 150
+    rnd = random.Random(11)
+    starts = [rnd.choice([149, 150, 383, 384, 1000, 2047, 4999]) for _ in range(n_seqs)]
+    slots = list(range(n_seqs))
+    rnd.shuffle(slots)
+    batch = make_batch(slots, starts, [1] * n_seqs)
+    cache = make_cache(n_seqs * width + 3, kv_heads, D, n_seqs, width, dtype, 90)
+    cache.window = window
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.k, ref_cache.v = cache.k.clone(), cache.v.clone()
+    qkv = rand((n_seqs, (heads + 2 * kv_heads) * D), dtype, 91)
+    qkv_ref = qkv.clone()
+    scale = 1.0 / math.sqrt(D)
+    got = ops.rope_attention(qkv, heads, kv_heads, D, None, None, 1e-6, None, None, batch, cache, scale, window)
+    want = ref.rope_attention(qkv_ref, heads, kv_heads, D, None, None, 1e-6, None, None, batch, ref_cache, scale, window)
+    ops.check()
+    assert torch.equal(cache.k, ref_cache.k) and torch.equal(cache.v, ref_cache.v)
+    close(got, want, dtype, f"TMA-fed decode attention round a wrapped ring {shape}")
+
+
 @pytest.mark.parametrize("shape", [(8, 2, 64), (32, 8, 128), (6, 2, 128), (5, 1, 64)])
 @pytest.mark.parametrize("window", [None, 100])
 def test_tcgen05_prefill_attention(ops, shape, window):
