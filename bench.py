@@ -279,7 +279,8 @@ def run_ours(args) -> dict:
     # tokens travel back with the kernels' error word. The reference's loop does the same (engine.py:458-469).
     e2e_value, e2e_ms, e2e_h2d = e2e_point(8)
     e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-           "h2d_bytes_per_step": round(e2e_h2d, 1), "d2h_bytes_per_step": (8 + 1) * 4, "points": {}}
+           "h2d_bytes_per_step": round(e2e_h2d, 1), "d2h_bytes_per_step": (8 + 1) * 4, "points": {},
+           "inputs": "prompts as host token lists; a decode step's input is the step before's output, handed on on the device"}
 
     # -- the other batch sizes -------------------------------------------------------
     points, point_clocks = {}, {}

@@ -130,3 +130,34 @@ def test_device_fed_steps_at_the_four_b_sizes(big_folder, sequences):
         cache.free(s)
     cache.check()
     engine.ops.check()
+
+
+def test_many_sequences_take_the_tma_fed_attention(big_folder):
+    """28 sequences x 8 kv heads are more (sequence, kv head) items than the cluster kernel is used for: the
+    single-token steps of this batch run the TMA-fed attention kernel inside the captured step. Lengths
+    straddle page boundaries (one sequence starts its third page during the steps); logits of several
+    requests against the plain implementation at every step."""
+    from kernel_rush_kawk_b200 import Engine, StepEntry
+
+    cfg, w = plain.read_folder(big_folder)
+    g = torch.Generator().manual_seed(8)
+    lengths = [5, 64, 63, 130, 127, 1, 70, 33] + [9 + 3 * i for i in range(20)]
+    steps = 4
+    seqs = [torch.randint(0, 151936, (n + steps,), generator=g).tolist() for n in lengths]
+    engine = Engine(big_folder, dtype="bfloat16", max_tokens=28 * 256, max_slots=28)
+    cache = engine.cache
+    slots = [cache.alloc() for _ in seqs]
+    checked = [1, 2, 3, 4, 5, 27]
+    refs = {i: plain.forward_logits(cfg, w, seqs[i], torch.float32, torch.bfloat16).float() for i in checked}
+    for i0 in range(0, 28, 7):  # prompts in four steps of seven requests
+        part = list(range(i0, i0 + 7))
+        engine.step([StepEntry(slots[i], seqs[i][:lengths[i]], []) for i in part])
+    for t in range(steps):
+        out = engine.step([StepEntry(slots[i], [seqs[i][lengths[i] + t]], [0]) for i in range(28)]).float().cpu()
+        for i in checked:
+            assert_close(out[i][None], refs[i][lengths[i] + t][None], "bfloat16", f"request {i} ({lengths[i]} tokens), decode step {t}")
+    assert engine.ops.use_tma_decode_attention
+    for s in slots:
+        cache.free(s)
+    cache.check()
+    engine.ops.check()
