@@ -18,6 +18,15 @@
 // reference's fused kernels compute it (gemm.py:22-51). Epilogue (swiglu): rows
 // n and N + n of W are gate and up; out = round(round(silu(round(g))) * round(u))
 // (gemm.py:108-113).
+//
+// A product with few output features (N of some thousands) has too few 16-row tiles to keep
+// every SM's memory pipe full: what bounds a block is the bytes it has in flight, and one block
+// of eight warps per SM holds 64 KB. Such products split K as well: the KSPLIT blocks of a
+// thread-block cluster stream a quarter of K each for the same tile, five small blocks share an
+// SM, and the partial sums meet in the first block's shared memory (distributed shared memory,
+// added in block order, so the result does not depend on timing).
+#include <cooperative_groups.h>
+
 #define KRK_TRACE_OWNER  // with -DKRK_TRACE this file keeps the timeline buffer
 #include "mma.cuh"
 
@@ -30,8 +39,13 @@ constexpr int RING_LOADS = 8;    // 16-row tile chunks in flight per thread (32 
 // a decode step at 16 sequences of the 4B shape: 2.79 ms against 3.08 ms with 8 (and 2.96 / 3.06 / 3.30 ms
 // with 5 / 7 / 4; the library product: 2.83 ms).
 constexpr int RING_LOADS_TWO_TILES = 6;
-template <int NT, bool NORM, bool DEEP>
-__host__ __device__ constexpr int ring_loads() { return (NT == 2 && !NORM) ? RING_LOADS_TWO_TILES : (DEEP ? 2 : 1) * RING_LOADS; }
+// five 4-warp blocks of a K-split product share an SM: 40 KB each with the ring, the reduction buffer and the inbox
+constexpr int RING_LOADS_KSPLIT = 6, RING_LOADS_KSPLIT_TWO_TILES = 4;
+template <int NT, bool NORM, bool DEEP, int KSPLIT = 1, int RING = 0>
+__host__ __device__ constexpr int ring_loads() {
+  return RING > 0 ? RING : (KSPLIT > 1) ? (NT == 2 ? RING_LOADS_KSPLIT_TWO_TILES : RING_LOADS_KSPLIT)
+                      : (NT == 2 && !NORM) ? RING_LOADS_TWO_TILES : (DEEP ? 2 : 1) * RING_LOADS;
+}
 
 // NT: 8-row batch tiles (1 or 2). RT: 16-row weight tiles per block; with SWIGLU the
 // block streams RT gate tiles and RT up tiles.
@@ -42,7 +56,7 @@ __host__ __device__ constexpr int ring_loads() { return (NT == 2 && !NORM) ? RIN
 // ring-full of copies is issued before anything else (before the wait on the
 // previous kernel, before the norm prologue), so the memory system is busy from the
 // block's first instruction.
-template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false>
+template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false, int KSPLIT = 1, int RING = 0>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ W,
               const bf16* __restrict__ branch, const void* __restrict__ gain, int gain_f32, bf16* __restrict__ x_new,
@@ -51,7 +65,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   KRK_TRACE_DECL
   constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;  // 16-row weight tiles this block streams
-  constexpr int STAGES = ring_loads<NT, NORM, DEEP>() / TILES;
+  constexpr int STAGES = ring_loads<NT, NORM, DEEP, KSPLIT, RING>() / TILES;
   constexpr int XSLOTS = NORM ? 0 : NT;          // without the prologue the batch rows ride in the ring too
   constexpr int SLOTS = TILES * 2 + XSLOTS;      // 16-byte pieces per thread and stage
   constexpr size_t RING_BYTES = (size_t)STAGES * SLOTS * THREADS * 16;
@@ -59,12 +73,16 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   float* red = reinterpret_cast<float*>(smem_raw + RING_BYTES);                       // [WARPS][TILES*NT*4*32]
   constexpr size_t RED_BYTES = (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
   bf16* xs = reinterpret_cast<bf16*>(smem_raw + RING_BYTES + RED_BYTES);              // [M][pitch] when NORM
+  float* inbox = reinterpret_cast<float*>(smem_raw + RING_BYTES + RED_BYTES);         // [KSPLIT - 1][outputs] (never with NORM)
+  static_assert(KSPLIT == 1 || (!NORM && !SWIGLU), "K is split only for the plain product");
+  if (KSPLIT > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "I have started"
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  const int ks = KSPLIT > 1 ? blockIdx.x % KSPLIT : 0;  // this block's part of K: its rank in the cluster
 
   // weight rows of this block's tiles, clamped so that edge tiles read valid memory
-  const int n0 = blockIdx.x * 16 * RT;
+  const int n0 = (blockIdx.x / KSPLIT) * 16 * RT;
   const bf16* wrow[TILES][2];
 #pragma unroll
   for (int s = 0; s < TILES; ++s) {
@@ -74,8 +92,10 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
     wrow[s][1] = W + (size_t)min(tile_row + g + 8, limit) * K + 8 * t;
   }
   const int n_chunks = K / CHUNK;
-  const int per_warp = (n_chunks + WARPS - 1) / WARPS;
-  const int c_begin = warp * per_warp, c_end = min(n_chunks, c_begin + per_warp);
+  const int per_block = (n_chunks + KSPLIT - 1) / KSPLIT;
+  const int b_begin = ks * per_block, b_end = min(n_chunks, b_begin + per_block);
+  const int per_warp = (max(0, b_end - b_begin) + WARPS - 1) / WARPS;
+  const int c_begin = b_begin + warp * per_warp, c_end = min(b_end, c_begin + per_warp);
   const int nc = max(0, c_end - c_begin);
 
   // batch rows of the B fragments when they come from global memory (no prologue)
@@ -239,6 +259,27 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
 
   // outputs of this block: RT*16 features x NT*8 batch rows
   constexpr int OUTS = RT * 16 * NT * 8;
+  if (KSPLIT > 1) {
+    // every block of the cluster but the first adds its warps' parts and puts the sums into the first block's
+    // inbox; one cluster barrier later the first block holds them all
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block of the cluster has started
+    if (ks != 0) {
+      float* dst = cluster.map_shared_rank(inbox, 0) + (size_t)(ks - 1) * OUTS;
+      for (int o = threadIdx.x; o < OUTS; o += THREADS) {
+        const int m = o % (NT * 8), f = o / (NT * 8);
+        const int tile = f / 16, r = f % 16;
+        const int j = m / 8, col = m % 8;
+        const int src_lane = (r % 8) * 4 + col / 2, reg = (r / 8) * 2 + (col & 1);
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += red[w * PER_WARP + ((tile * NT + j) * 4 + reg) * 32 + src_lane];
+        dst[o] = v;
+      }
+    }
+    cluster.sync();
+  }
   for (int o = threadIdx.x; o < OUTS; o += THREADS) {
     const int m = o % (NT * 8), f = o / (NT * 8);  // batch row, feature within the block
     const int tile = f / 16, r = f % 16;
@@ -250,6 +291,14 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
     for (int w = 0; w < WARPS; ++w) {
       v += red[w * PER_WARP + ((tile * NT + j) * 4 + reg) * 32 + src_lane];
       if (SWIGLU) v2 += red[w * PER_WARP + (((RT + tile) * NT + j) * 4 + reg) * 32 + src_lane];
+    }
+    if (KSPLIT > 1) {
+      if (ks == 0) {
+#pragma unroll
+        for (int r = 0; r < KSPLIT - 1; ++r) v += inbox[r * OUTS + o];  // the other blocks' parts, in block order
+      } else {
+        continue;
+      }
     }
     const int n = n0 + f;
     if (m < M && n < N) {
@@ -263,27 +312,47 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   KRK_TRACE_END(K)
 }
 
-template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false>
+template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false, int KSPLIT = 1, int RING = 0>
 int launch_warps(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
   constexpr int THREADS = WARPS * 32;
   constexpr int TILES = SWIGLU ? 2 * RT : RT;
-  constexpr int STAGES = ring_loads<NT, NORM, DEEP>() / TILES;
+  constexpr int STAGES = ring_loads<NT, NORM, DEEP, KSPLIT, RING>() / TILES;
   int pitch = 0;
   constexpr int SLOTS = TILES * 2 + (NORM ? 0 : NT);
-  size_t smem = (size_t)STAGES * SLOTS * THREADS * 16 + (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float);
+  size_t smem = (size_t)STAGES * SLOTS * THREADS * 16 + (size_t)WARPS * TILES * NT * 4 * 32 * sizeof(float) +
+                (size_t)(KSPLIT - 1) * RT * 16 * NT * 8 * sizeof(float);
   if (NORM) {
     const int pad_bytes = (64 - (K * 2) % 128 + 128) % 128;
     pitch = K + pad_bytes / 2;
     smem += (size_t)M * pitch * 2;
   }
   if (smem > 220 * 1024) return -2;
-  auto kern = skinny_kernel<WARPS, NT, RT, SWIGLU, NORM, TOut, DEEP>;
+  auto kern = skinny_kernel<WARPS, NT, RT, SWIGLU, NORM, TOut, DEEP, KSPLIT, RING>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
+  if (KSPLIT > 1) {  // the blocks of a cluster share a tile and split K
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks * KSPLIT);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KSPLIT;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    static const bool plain = getenv("KRK_NO_PDL") != nullptr;
+    cfg.attrs = attr;
+    cfg.numAttrs = plain ? 1 : 2;
+    return (int)cudaLaunchKernelEx(&cfg, kern, (TOut*)out, (const bf16*)x, (const bf16*)W, (const bf16*)branch, gain, gain_f32,
+                                   (bf16*)x_new, M, N, K, eps, pitch);
+  }
   cudaError_t e = launch_pdl(kern, dim3(blocks), dim3(THREADS), smem, stream, (TOut*)out, (const bf16*)x, (const bf16*)W,
                              (const bf16*)branch, gain, gain_f32, (bf16*)x_new, M, N, K, eps, pitch);
   if (e != cudaSuccess) return (int)e;
@@ -297,8 +366,24 @@ template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
 int launch(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
+  // Between two and three blocks per SM: small blocks, but with rings as deep as three of them fit beside one
+  // another, since what bounds a block is the bytes it has in flight.
+  if constexpr (!SWIGLU && RT == 1) {
+    static const bool no_deep = getenv("KRK_NO_DEEP_RING") != nullptr;  // measurement switch
+    if (!no_deep && blocks > 2 * 148 && blocks <= 3 * 148)
+      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 14 : NT == 1 ? 11 : 8)>(
+          out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  }
   if (blocks > 2 * 148 && blocks <= 5 * 148)
     return launch_warps<4, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  // few tiles (about one per SM): split K four ways over a cluster, so that four to five small blocks an SM
+  // have their bytes in flight instead of one large one
+  if constexpr (!SWIGLU && !NORM && RT == 1) {
+    static const bool no_ksplit = getenv("KRK_NO_KSPLIT") != nullptr;  // measurement switch
+    if (!no_ksplit && blocks * 4 <= 5 * 148 && K >= 4 * 4 * CHUNK * 4)
+      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 4>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps,
+                                                                    stream);
+  }
   // (a ring twice as deep for kernels of about one block per SM was measured: slower, because the
   // next kernel's blocks then no longer fit beside it to prefetch their weights)
   return launch_warps<8, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);

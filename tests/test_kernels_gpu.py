@@ -92,6 +92,23 @@ def test_linear(ops, dtype, mnk):
     close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), dtype, f"linear {mnk}, float32 out")
 
 
+@pytest.mark.parametrize("mnk", [(1, 2560, 9728), (8, 2560, 4096), (16, 2560, 9728), (13, 1000, 2080), (3, 48, 2048),
+                                 (9, 2000, 4128)])
+def test_few_row_products_that_split_k_over_a_cluster(ops, mnk):
+    """Few output features and a long K: the bfloat16 product splits K over the four blocks of a cluster and adds
+    the parts in the first block's shared memory. Sizes off the grid (features no multiple of 16, chunks that do
+    not divide by four), both output types, and the same bits on every run."""
+    m, n, k = mnk
+    dtype = torch.bfloat16
+    x, w = rand((m, k), dtype, 84), rand((n, k), dtype, 85, 0.05)
+    ref = TorchOps(dtype)
+    got = ops.linear(x, w)
+    close(got, ref.linear(x, w), dtype, f"linear {mnk}")
+    close(ops.linear(x, w, out_float32=True), ref.linear(x, w, out_float32=True), dtype, f"linear {mnk}, float32 out")
+    for _ in range(3):
+        assert torch.equal(ops.linear(x, w), got), "the sum over the cluster's parts must not depend on timing"
+
+
 @pytest.mark.parametrize("mnk", [(128, 128, 64), (128, 128, 512), (256, 384, 2560), (130, 200, 72), (77, 3000, 1000),
                                  (2048, 2560, 4096)])
 def test_tcgen05_gemm(ops, mnk):
