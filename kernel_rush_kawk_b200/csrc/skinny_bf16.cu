@@ -369,8 +369,7 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
   // Between two and three blocks per SM: small blocks, but with rings as deep as three of them fit beside one
   // another, since what bounds a block is the bytes it has in flight.
   if constexpr (!SWIGLU && RT == 1) {
-    static const bool no_deep = getenv("KRK_NO_DEEP_RING") != nullptr;  // measurement switch
-    if (!no_deep && blocks > 2 * 148 && blocks <= 3 * 148)
+    if (blocks > 2 * 148 && blocks <= 3 * 148)
       return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 14 : NT == 1 ? 11 : 8)>(
           out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
   }
@@ -379,8 +378,7 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
   // few tiles (about one per SM): split K four ways over a cluster, so that four to five small blocks an SM
   // have their bytes in flight instead of one large one
   if constexpr (!SWIGLU && !NORM && RT == 1) {
-    static const bool no_ksplit = getenv("KRK_NO_KSPLIT") != nullptr;  // measurement switch
-    if (!no_ksplit && blocks * 4 <= 5 * 148 && K >= 4 * 4 * CHUNK * 4)
+    if (blocks * 4 <= 5 * 148 && K >= 4 * 4 * CHUNK * 4)
       return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 4>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps,
                                                                     stream);
   }
