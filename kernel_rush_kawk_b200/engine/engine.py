@@ -148,7 +148,12 @@ class Engine:
     def generate(self, input_ids, max_new_tokens: int, *, temperature: float = 0.0, seed: int = 0,
                  stop_token_ids=()):
         """Yield, per step, one token id per sequence (None once a sequence has ended
-        on a stop token). All sequences start together; their lengths may differ."""
+        on a stop token). All sequences start together; their lengths may differ.
+
+        This is a generator: arguments are checked, and a cache without a fixed size is
+        grown if the call needs more room, at the first ``next()``. One generation runs
+        at a time: growing the cache while an earlier generator still holds sequences
+        raises."""
         prompts = [list(map(int, row)) for row in input_ids]
         if max_new_tokens < 1 or not prompts:
             return
