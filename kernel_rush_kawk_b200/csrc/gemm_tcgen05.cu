@@ -34,7 +34,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int NB = SWIGLU ? 2 : 1;                       // weight tiles per stage
   constexpr uint32_t B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + NB * B_BYTES;
-  constexpr uint32_t TMEM_COLS = NB * BN;                  // 128, 256 or 512: a power of two
+  constexpr uint32_t TMEM_COLS = NB * BN <= 128 ? 128 : NB * BN <= 256 ? 256 : 512;  // a power of two
+  constexpr int WBOX = (BN % 128 == 0) ? 128 : BN / 2;     // rows of a weight box (192- and 224-wide tiles: two boxes)
   // 1024-byte alignment of every tile: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * STAGE_BYTES);
@@ -72,11 +73,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_expect_tx(full_bar + s, STAGE_BYTES);
       tma_load_2d(stage, &map_a, full_bar + s, kb * BK, m0);
 #pragma unroll
-      for (int h = 0; h < BN / 128; ++h) {  // the weight box has 128 rows
-        tma_load_2d(stage + A_BYTES + h * (128 * BK * 2), &map_w, full_bar + s, kb * BK, n0 + 128 * h);
+      for (int h = 0; h < BN / WBOX; ++h) {
+        tma_load_2d(stage + A_BYTES + h * (WBOX * BK * 2), &map_w, full_bar + s, kb * BK, n0 + WBOX * h);
         if (SWIGLU)
-          tma_load_2d(stage + A_BYTES + B_BYTES + h * (128 * BK * 2), &map_w, full_bar + s, kb * BK,
-                      up_row_offset + n0 + 128 * h);
+          tma_load_2d(stage + A_BYTES + B_BYTES + h * (WBOX * BK * 2), &map_w, full_bar + s, kb * BK,
+                      up_row_offset + n0 + WBOX * h);
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -168,10 +169,10 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, 
   CUtensorMap map_a, map_w;
   int rc = make_map_bf16(&map_a, A, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map_bf16(&map_w, W, SWIGLU ? 2 * N : N, K, ldw, 128);
+  rc = make_map_bf16(&map_w, W, SWIGLU ? 2 * N : N, K, ldw, (BN % 128 == 0) ? 128 : BN / 2);
   if (rc) return rc;
   auto kern = gemm_tcgen05_kernel<SWIGLU, BN, STAGES, TOut>;
-  static bool configured = false;
+  static bool configured = false;  // one flag per instantiation of this template
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -198,6 +199,19 @@ KRK_API int krk_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N
   //          1 = 128x128 tile, three stages, two blocks per SM
   if (out_f32) {  // float32 output (output-head logits); no activation
     if (swiglu) return -4;
+    // One tile per block and one block per SM: the time is rounds of blocks x tile width. A vocabulary that leaves
+    // the last round of 256-wide tiles nearly empty is served faster by narrower tiles that fill their rounds
+    // (151,936 columns at up to 128 rows: 594 tiles of 256 = five rounds, 679 of 224 = five shorter ones).
+    int sms = 148;
+    {
+      int dev = 0;
+      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const long long row_tiles = (M + BM - 1) / BM;
+    auto cost = [&](int bn) { return ((row_tiles * ((N + bn - 1) / bn) + sms - 1) / sms) * bn; };
+    if (cost(224) < cost(256) && cost(224) <= cost(192))
+      return launch<false, 224, 4, float>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
+    if (cost(192) < cost(256)) return launch<false, 192, 4, float>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
     return launch<false, 256, 4, float>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);
   }
   if (swiglu) return launch<true, 128, 4, bf16>(C, A, W, M, N, K, lda, ldw, ldc, error, stream);

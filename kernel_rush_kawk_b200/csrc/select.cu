@@ -40,11 +40,10 @@ __global__ void select_scan_kernel(unsigned long long* __restrict__ packed, cons
   const bool sample = temperature > 0.f;
   uint32_t key = 0;
   if (sample) key = mix32(mix32(mix32(seed) ^ (uint32_t)requests[row]) ^ step);
-  const int per = (vocab + gridDim.x - 1) / gridDim.x;
+  const int per = (((vocab + gridDim.x - 1) / gridDim.x) + 3) & ~3;  // a multiple of four: chunks start on 16 bytes
   const int begin = blockIdx.x * per, end = min(vocab, begin + per);
   unsigned long long best = 0;
-  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    float v = x[i];
+  auto take = [&](float v, int i) {
     if (sample) {
       const uint32_t h = mix32(key ^ ((uint32_t)i * 0x9E3779B9u));
       const float u = ((float)(h >> 9) + 0.5f) * (1.0f / 8388608.0f);
@@ -52,6 +51,17 @@ __global__ void select_scan_kernel(unsigned long long* __restrict__ packed, cons
     }
     const unsigned long long cand = ((unsigned long long)ordered_bits(v) << 32) | (uint32_t)(~(uint32_t)i);
     best = cand > best ? cand : best;
+  };
+  if ((vocab & 3) == 0 && ((uintptr_t)logits & 15) == 0) {  // rows start on 16 bytes: four logits per load
+    for (int i = begin + 4 * threadIdx.x; i < end; i += 4 * blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(x + i);
+      take(v.x, i);
+      take(v.y, i + 1);
+      take(v.z, i + 2);
+      take(v.w, i + 3);
+    }
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) take(x[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -121,6 +121,17 @@ def test_tcgen05_gemm(ops, mnk):
     ops.check()
 
 
+def test_tcgen05_logits_tiles_of_every_width(ops):
+    """Float32 logits take 256-, 224- or 192-wide tiles, whichever fills its rounds of blocks best: a vocabulary of
+    151,936 at up to 128 rows takes 224, 3,000 columns take 192, 148 x 256 columns take 256."""
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    for m, n, k in ((64, 151936, 64), (20, 3000, 96), (33, 148 * 256, 64)):
+        x, w = rand((m, k), dtype, 86), rand((n, k), dtype, 87, 0.05)
+        close(ops.gemm_tcgen05(x, w, out_float32=True), ref.linear(x, w, out_float32=True), dtype, f"logits {m} x {n} x {k}")
+    ops.check()
+
+
 @pytest.mark.parametrize("mik", [(128, 128, 128), (300, 272, 160), (2048, 9728, 2560)])
 def test_tcgen05_gemm_with_swiglu_epilogue(ops, mik):
     m, inter, k = mik
