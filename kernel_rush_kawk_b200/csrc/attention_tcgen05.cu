@@ -50,6 +50,7 @@ constexpr uint32_t TILE_BYTES = DB * SUB;  // a Q, K or V tile
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_O = 256;       // O_t starts at column 256 + t * D; S_t at t * 128
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int PAGE_IDS = 1024;         // page-table entries a block keeps in shared memory (64 K keys)
 constexpr float RESCALE_STEP = 8.f;    // in log2 units: the reference maximum moves when outgrown by 2^8
 
 enum Bar { K_FULL = 0, V_FULL = 2, K_FREE = 4, V_FREE = 6, S_FULL = 8, P_READY = 10, O_DONE = 12, Q_FULL = 14, N_BARS = 15 };
@@ -91,6 +92,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   unsigned char* v_s = k_s + 2 * TILE_BYTES;    // two stages
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  int* pages_s = reinterpret_cast<int*>(tmem_slot + 2);  // [PAGE_IDS] the block's page-table entries, from page 2 * j_lo on
 
   // blockIdx.x counts (row pair, kv head) with the pair as the slow index, descending: blocks start in
   // launch order, so the pairs with the most key blocks, of every kv head, run first and the short ones
@@ -115,7 +117,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     mbar_expect_tx(bar, TILE_BYTES);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int page = table[(size_t)slot * width + (2 * (j_lo + i) + half) % width];
+      // from shared memory: a load from the page table here would stand between the issuing thread's MMAs
+      const int at = 2 * i + half;
+      const int page = at < PAGE_IDS ? pages_s[at] : table[(size_t)slot * width + (2 * (j_lo + i) + half) % width];
       const int row = (page * HKV + kh) * KRK_PAGE;
 #pragma unroll
       for (int h = 0; h < DB; ++h) tma_load_2d(dst + h * SUB + half * (64 * 128), map, bar, h * 64, row);
@@ -125,6 +129,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   auto load_v = [&](int i) { load_tile(v_s + (i & 1) * TILE_BYTES, &map_v, bars + V_FULL + (i & 1), i); };
 
   if (warp == 8) {
+    for (int i = lane; i < min(2 * n, PAGE_IDS); i += 32) pages_s[i] = table[(size_t)slot * width + (2 * j_lo + i) % width];
+    __syncwarp();
     if (lane == 0) {
       for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -363,7 +369,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
-constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64;
+constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64 + PAGE_IDS * sizeof(int);
 
 }  // namespace
 
