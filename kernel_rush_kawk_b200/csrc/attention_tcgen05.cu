@@ -14,6 +14,8 @@
 //   S = Q K^T                                   [issuer]   -> s_full
 //   row max; p = exp2(S*c - m) rounded to bfloat16 -> tensor memory  [softmax]  -> p_ready
 //   O += P V   (V as an MN-major B operand)     [issuer]
+// The softmax reads S twice, 64 columns at a time (first for the maximum, then for the probabilities):
+// 128 scores a thread would spill registers, and a tensor-memory load is cheap.
 // O stays in tensor memory across key blocks. The reference maximum m of a row moves only when the
 // row's maximum has grown by more than 2^8 since it was set (then the warp rescales its O rows in
 // tensor memory); until then p <= 2^8, which float32 sums and bfloat16 probabilities hold without
@@ -43,6 +45,7 @@ constexpr int D = KRK_HEAD_DIM;
 constexpr int ROWS = 128;              // query rows per tile
 constexpr int PAIR = 2 * ROWS;         // query rows per block
 constexpr int KEYS = 128;              // keys per block iteration: two pages
+constexpr int HALF = KEYS / 2;         // score columns a softmax thread holds at a time
 constexpr int DB = D / 64;             // 64-wide blocks of the head dimension
 constexpr int THREADS = 288;           // 2 x 4 softmax warps + the issuing warp
 constexpr uint32_t SUB = 128 * 128;    // bytes of a [128 rows x 64 bf16] swizzled sub-tile
@@ -267,20 +270,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       // tensor-memory loads and stores are warp-wide: the whole warp gives up together
       if (!__all_sync(0xffffffffu, mbar_wait(bars + S_FULL + t, c & 1))) { if (lane == 0) atomicExch(error, 12); ok = false; break; }
       tc_fence_after();
-      uint32_t s[KEYS];
+      // the row sees keys first..first + span of the block: (unsigned)(i - first) <= span; none of them: no i passes
+      const bool whole = key0 + KEYS - 1 <= pos && key0 >= lo;
+      const bool none = pos < max(lo, key0);
+      const unsigned first = none ? (unsigned)KEYS : (unsigned)max(lo - key0, 0);
+      const unsigned span = none ? 0u : (unsigned)(pos - key0) - first;
+      // two passes over S, 64 columns at a time (a row's 128 scores held at once spill registers): the maximum
+      // first, then the probabilities. P's first half lands on columns of S that both passes are done with.
+      auto load_half = [&](int half, uint32_t (&s)[HALF]) {
+        __syncwarp();  // rows that see the whole block and rows at its edge take different paths between the loads
 #pragma unroll
-      for (int q = 0; q < KEYS / 32; ++q) tmem_ld_32x32(tmem_s + 32 * q, *reinterpret_cast<uint32_t(*)[32]>(s + 32 * q));
-      tmem_wait_ld();
-      const bool whole = key0 + KEYS - 1 <= pos && key0 >= lo;  // the row sees every key of the block
+        for (int q = 0; q < HALF / 32; ++q) tmem_ld_32x32(tmem_s + HALF * half + 32 * q, *reinterpret_cast<uint32_t(*)[32]>(s + 32 * q));
+        tmem_wait_ld();
+      };
       float mx = -INFINITY;
-      if (whole) {
 #pragma unroll
-        for (int i = 0; i < KEYS; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-      } else {
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[HALF];
+        load_half(half, s);
+        if (whole) {
 #pragma unroll
-        for (int i = 0; i < KEYS; ++i) {
-          const int key = key0 + i;
-          if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(s[i]));
+          for (int i = 0; i < HALF; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < HALF; ++i)
+            if ((unsigned)(HALF * half + i) - first <= span) mx = fmaxf(mx, __uint_as_float(s[i]));
         }
       }
       const float m_new = fmaxf(m, mx * scale_log2);
@@ -305,31 +319,34 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       }
       const float m_safe = m == -INFINITY ? 0.f : m;
       float sum = 0.f;
-      uint32_t pk[KEYS / 2];
-      if (whole) {
 #pragma unroll
-        for (int i = 0; i < KEYS; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe));
-          sum += p0 + p1;
-          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-      } else {
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[HALF], pk[HALF / 2];
+        load_half(half, s);
+        if (whole) {
 #pragma unroll
-        for (int i = 0; i < KEYS; i += 2) {
-          const int key = key0 + i;
-          const float p0 = (key <= pos && key >= lo) ? fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe)) : 0.f;
-          const float p1 = (key + 1 <= pos && key + 1 >= lo) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe)) : 0.f;
-          sum += p0 + p1;
-          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          for (int i = 0; i < HALF; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe));
+            sum += p0 + p1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < HALF; i += 2) {
+            const unsigned at = (unsigned)(HALF * half + i);
+            const float p0 = (at - first <= span) ? fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe)) : 0.f;
+            const float p1 = (at + 1 - first <= span) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe)) : 0.f;
+            sum += p0 + p1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          }
         }
+        __syncwarp();
+        tmem_st_32x32(tmem_s + (HALF / 2) * half, pk);
       }
       l += sum;
-      __syncwarp();  // rows that see the whole block and rows at its edge took different paths
-#pragma unroll
-      for (int q = 0; q < KEYS / 64; ++q) tmem_st_32x32(tmem_s + 32 * q, *reinterpret_cast<const uint32_t(*)[32]>(pk + 32 * q));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars + P_READY + t);
