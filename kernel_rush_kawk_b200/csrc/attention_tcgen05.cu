@@ -6,16 +6,17 @@
 //   64 columns of S_t (two keys per 32-bit column) and is the A operand of O_t += P_t V.
 //   shared memory: Q0, Q1, and K and V double-buffered (128-byte swizzle, filled by TMA).
 //
-// Warps 0..3 run the softmax of tile 0, warps 4..7 that of tile 1 (thread = query row = tensor-memory
-// lane); lane 0 of warp 8 issues every TMA load and every MMA, in the order
+// Warps 0..7 run the softmax of tile 0 and of tile 1 in turn (thread = query row = tensor-memory lane,
+// and one half of the block's keys: warps w and w + 4 share their rows); lane 0 of warp 8 issues every
+// MMA (lane 0 of warp 9 the TMA loads), in the order
 //   ... PV0(j-1) QK0(j) PV1(j-1) QK1(j) PV0(j) QK0(j+1) ...
-// so that while one tile's rows are in the softmax the tensor core works for the other tile.
+// so that while one tile's rows are in the softmax the tensor core works for the other tile. A tile's
+// next MMAs wait for its softmax, so all eight warps on one tile (half the time per block) shorten the
+// chain that bounds the kernel: softmax of a block, its P V, the next block's Q K^T.
 // Per key block of 128 keys (two cache pages) and tile:
 //   S = Q K^T                                   [issuer]   -> s_full
 //   row max; p = exp2(S*c - m) rounded to bfloat16 -> tensor memory  [softmax]  -> p_ready
 //   O += P V   (V as an MN-major B operand)     [issuer]
-// The softmax reads S twice, 64 columns at a time (first for the maximum, then for the probabilities):
-// 128 scores a thread would spill registers, and a tensor-memory load is cheap.
 // O stays in tensor memory across key blocks. The reference maximum m of a row moves only when the
 // row's maximum has grown by more than 2^8 since it was set (then the warp rescales its O rows in
 // tensor memory); until then p <= 2^8, which float32 sums and bfloat16 probabilities hold without
@@ -47,7 +48,7 @@ constexpr int PAIR = 2 * ROWS;         // query rows per block
 constexpr int KEYS = 128;              // keys per block iteration: two pages
 constexpr int HALF = KEYS / 2;         // score columns a softmax thread holds at a time
 constexpr int DB = D / 64;             // 64-wide blocks of the head dimension
-constexpr int THREADS = 288;           // 2 x 4 softmax warps + the issuing warp
+constexpr int THREADS = 320;           // 8 softmax warps, the warp that issues the MMAs, the warp that loads
 constexpr uint32_t SUB = 128 * 128;    // bytes of a [128 rows x 64 bf16] swizzled sub-tile
 constexpr uint32_t TILE_BYTES = DB * SUB;  // a Q, K or V tile
 constexpr uint32_t TMEM_COLS = 512;
@@ -96,6 +97,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
   int* pages_s = reinterpret_cast<int*>(tmem_slot + 2);  // [PAGE_IDS] the block's page-table entries, from page 2 * j_lo on
+  float* xchg = reinterpret_cast<float*>(pages_s + PAGE_IDS);  // [2 copies][2 halves][ROWS] partial row maxima of the softmax warps
+  float* xsum = xchg + 4 * ROWS;                               // [2 tiles][2 halves][ROWS] their partial row sums
+  volatile int* gave_up = reinterpret_cast<volatile int*>(xsum + 4 * ROWS);  // [4] per pair of softmax warps
 
   // blockIdx.x counts (row pair, kv head) with the pair as the slow index, descending: blocks start in
   // launch order, so the pairs with the most key blocks, of every kv head, run first and the short ones
@@ -115,7 +119,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const int j_hi = r1.lo <= r1.hi ? max(r0.hi, r1.hi) : r0.hi;
   const int n = j_hi - j_lo + 1;
 
-  // TMA loads of the issuer (warp 8, lane 0); the first of them start before the block's first barrier
+  // TMA loads: the first ones by the issuer (warp 8, lane 0) before the block's first barrier, the rest by the loader
   auto load_tile = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int i) {
     mbar_expect_tx(bar, TILE_BYTES);
 #pragma unroll
@@ -135,11 +139,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     for (int i = lane; i < min(2 * n, PAGE_IDS); i += 32) pages_s[i] = table[(size_t)slot * width + (2 * j_lo + i) % width];
     __syncwarp();
     if (lane == 0) {
-      for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? ROWS : 1);
+      for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? 2 * ROWS : 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       // a block of this step that gave up on a wait (codes from 3 on): the others do no work. The host reads and
       // clears the word at the end of every step, so a flag never outlives the step that raised it.
       tmem_slot[1] = (uint32_t)(*reinterpret_cast<volatile int*>(error) >= 3);
+      for (int i = 0; i < 4; ++i) gave_up[i] = 0;
       if (q_by_tma) {
         // a query tile is a box of 128 / G tokens x G heads x 64 dims per 64-wide block of the head: its rows
         // land in (token, group member) order, which is the tile's row order
@@ -213,10 +218,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       }
       for (int i = 0; i < n && ok; ++i) {
         const int j = j_lo + i, b = i & 1;
-        if (i + 1 < n) {  // V of the next block goes where block i - 1's was
-          if (i >= 1 && !mbar_wait(bars + V_FREE + ((i + 1) & 1), ((i - 1) >> 1) & 1)) { give_up(7); break; }
-          load_v(i + 1);
-        }
         bool v_ready = false, k_ready = false;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
@@ -243,86 +244,111 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
             if (t == 1) umma_commit(bars + K_FREE + ((i + 1) & 1));
           }
         }
-        if (ok && i + 2 < n) {  // K of block i + 2 goes where block i's was
-          if (!mbar_wait(bars + K_FREE + b, (i >> 1) & 1)) { give_up(11); break; }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      // ---- loader: the TMA loads after the first ones. A thread of its own: issuing a load takes the time of
+      // several MMAs, and the issuer's instruction stream is what bounds the kernel.
+      for (int i = 0; i < n; ++i) {
+        if (i + 1 < n) {  // V of the next block goes where block i - 1's was
+          if (i >= 1 && !mbar_wait(bars + V_FREE + ((i + 1) & 1), ((i - 1) >> 1) & 1)) { atomicExch(error, 7); break; }
+          load_v(i + 1);
+        }
+        if (i + 2 < n) {  // K of block i + 2 goes where block i's was
+          if (!mbar_wait(bars + K_FREE + (i & 1), (i >> 1) & 1)) { atomicExch(error, 11); break; }
           load_k(i + 2);
         }
       }
     }
   } else {
-    // ---- softmax: thread = row of tile t ----
-    const int t = warp >> 2;
-    const TileRange rng = t == 0 ? r0 : r1;
-    const int r = threadIdx.x - t * ROWS;
-    const int R = pair * PAIR + t * ROWS + r;
-    const bool valid = R < n_rows;
-    const int tok = valid ? R / G : 0;
-    const int pos = valid ? start + tok : -1;  // -1: sees nothing
-    const int lo = (valid && window > 0) ? max(0, pos - window + 1) : 0;
-    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tmem_s = tmem + t * 128 + lane_addr;
-    const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
-    float m = -INFINITY, l = 0.f;
+    // ---- softmax: all eight warps work on one tile at a time, tile 0 and tile 1 in turn. Thread = query row r of
+    // both tiles (its tensor-memory lane) and one half of a block's keys: warps w and w + 4 share the rows
+    // 32 (w & 3) .. + 31 and exchange their partial row maxima (and, at the end, sums) through shared memory.
+    // A tile's block is through the softmax in half the time, which is what the other tile's MMAs wait for.
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const TileRange rng[2] = {r0, r1};
+    bool valid[2];
+    int tok[2], pos[2], lo[2];
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int R = pair * PAIR + t * ROWS + r;
+      valid[t] = R < n_rows;
+      tok[t] = valid[t] ? R / G : 0;
+      pos[t] = valid[t] ? start + tok[t] : -1;  // -1: sees nothing
+      lo[t] = (valid[t] && window > 0) ? max(0, pos[t] - window + 1) : 0;
+    }
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
     bool ok = true;
-    for (int j = rng.lo; j <= rng.hi; ++j) {
-      const uint32_t c = (uint32_t)(j - rng.lo);
-      const int key0 = j * KEYS;
-      // tensor-memory loads and stores are warp-wide: the whole warp gives up together
-      if (!__all_sync(0xffffffffu, mbar_wait(bars + S_FULL + t, c & 1))) { if (lane == 0) atomicExch(error, 12); ok = false; break; }
-      tc_fence_after();
-      // the row sees keys first..first + span of the block: (unsigned)(i - first) <= span; none of them: no i passes
-      const bool whole = key0 + KEYS - 1 <= pos && key0 >= lo;
-      const bool none = pos < max(lo, key0);
-      const unsigned first = none ? (unsigned)KEYS : (unsigned)max(lo - key0, 0);
-      const unsigned span = none ? 0u : (unsigned)(pos - key0) - first;
-      // two passes over S, 64 columns at a time (a row's 128 scores held at once spill registers): the maximum
-      // first, then the probabilities. P's first half lands on columns of S that both passes are done with.
-      auto load_half = [&](int half, uint32_t (&s)[HALF]) {
-        __syncwarp();  // rows that see the whole block and rows at its edge take different paths between the loads
+    uint32_t step = 0;
+    for (int j = j_lo; j <= j_hi && ok; ++j) {
 #pragma unroll
-        for (int q = 0; q < HALF / 32; ++q) tmem_ld_32x32(tmem_s + HALF * half + 32 * q, *reinterpret_cast<uint32_t(*)[32]>(s + 32 * q));
-        tmem_wait_ld();
-      };
-      float mx = -INFINITY;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int t = 0; t < 2; ++t) {
+        if (j < rng[t].lo || j > rng[t].hi) continue;  // the same for every thread of the block
+        const uint32_t c = (uint32_t)(j - rng[t].lo);
+        const int key0 = j * KEYS + half * HALF;  // this thread's first key
+        const uint32_t tmem_s = tmem + t * 128 + lane_addr;
+        const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
+        float* xm = xchg + (step & 1) * 2 * ROWS;  // [half][row], two copies used in turn
+        ++step;
+        // the row sees keys first..first + span of its half: (unsigned)(i - first) <= span; none of them: no i passes
+        const bool whole = key0 + HALF - 1 <= pos[t] && key0 >= lo[t];
+        const bool none = pos[t] < max(lo[t], key0);
+        const unsigned first = none ? (unsigned)HALF : (unsigned)max(lo[t] - key0, 0);
+        const unsigned span = none ? 0u : (unsigned)(pos[t] - key0) - first;
+        // tensor-memory loads and stores are warp-wide, and the two warps of a row meet at a barrier that has no
+        // time limit: a warp that gives up says so in shared memory and both leave after the barrier
+        const bool arrived = __all_sync(0xffffffffu, mbar_wait(bars + S_FULL + t, c & 1));
         uint32_t s[HALF];
-        load_half(half, s);
-        if (whole) {
+        float mx = -INFINITY;
+        if (arrived) {
+          tc_fence_after();
 #pragma unroll
-          for (int i = 0; i < HALF; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < HALF; ++i)
-            if ((unsigned)(HALF * half + i) - first <= span) mx = fmaxf(mx, __uint_as_float(s[i]));
-        }
-      }
-      const float m_new = fmaxf(m, mx * scale_log2);
-      const bool outgrown = m != -INFINITY && m_new - m > RESCALE_STEP;
-      if (__any_sync(0xffffffffu, outgrown)) {
-        // the warp moves its rows' reference maxima; the block's P.V has not been issued and the one before
-        // it is complete (S of this block came after it), so nothing else touches these rows of O
-        const float alpha = m == -INFINITY ? 1.f : fast_exp2(m - m_new);
-#pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32(tmem_o + c0, o);
+          for (int q = 0; q < HALF / 32; ++q) tmem_ld_32x32(tmem_s + HALF * half + 32 * q, *reinterpret_cast<uint32_t(*)[32]>(s + 32 * q));
           tmem_wait_ld();
+          if (whole) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32(tmem_o + c0, o);
+            for (int i = 0; i < HALF; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < HALF; ++i)
+              if ((unsigned)i - first <= span) mx = fmaxf(mx, __uint_as_float(s[i]));
+          }
+          xm[half * ROWS + r] = mx;
+        } else if (lane == 0) {
+          atomicExch(error, 12);
+          gave_up[quad] = 1;
         }
-        l *= alpha;
-        m = m_new;
-      } else if (m == -INFINITY) {
-        m = m_new;  // no key seen before this block: O and l are still zero
-      }
-      const float m_safe = m == -INFINITY ? 0.f : m;
-      float sum = 0.f;
+        pair_sync();
+        if (gave_up[quad]) { ok = false; break; }
+        mx = fmaxf(mx, xm[(half ^ 1) * ROWS + r]);
+        const float m_new = fmaxf(m[t], mx * scale_log2);
+        const bool outgrown = m[t] != -INFINITY && m_new - m[t] > RESCALE_STEP;
+        if (__any_sync(0xffffffffu, outgrown)) {
+          // the warp moves its rows' reference maxima (its partner, with the same rows and maxima, decides the
+          // same) and scales its half of the columns of O; the block's P.V has not been issued and the one
+          // before it is complete (S of this block came after it), so nothing else touches these rows of O
+          const float alpha = m[t] == -INFINITY ? 1.f : fast_exp2(m[t] - m_new);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[HALF], pk[HALF / 2];
-        load_half(half, s);
+          for (int c0 = 0; c0 < D / 2; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_o + half * (D / 2) + c0, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_o + half * (D / 2) + c0, o);
+          }
+          l[t] *= alpha;
+          m[t] = m_new;
+        } else if (m[t] == -INFINITY) {
+          m[t] = m_new;  // no key seen before this block: O and l are still zero
+        }
+        const float m_safe = m[t] == -INFINITY ? 0.f : m[t];
+        float sum = 0.f;
+        uint32_t pk[HALF / 2];
         if (whole) {
 #pragma unroll
           for (int i = 0; i < HALF; i += 2) {
@@ -335,35 +361,44 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         } else {
 #pragma unroll
           for (int i = 0; i < HALF; i += 2) {
-            const unsigned at = (unsigned)(HALF * half + i);
-            const float p0 = (at - first <= span) ? fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe)) : 0.f;
-            const float p1 = (at + 1 - first <= span) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe)) : 0.f;
+            const float p0 = ((unsigned)i - first <= span) ? fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_safe)) : 0.f;
+            const float p1 = ((unsigned)(i + 1) - first <= span) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_safe)) : 0.f;
             sum += p0 + p1;
             const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
             pk[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
           }
         }
-        __syncwarp();
+        l[t] += sum;
+        __syncwarp();  // rows that see their whole half and rows at its edge took different paths
+        // P's second half lands on score columns of the partner warp, which holds them in registers since the barrier
         tmem_st_32x32(tmem_s + (HALF / 2) * half, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bars + P_READY + t);
       }
-      l += sum;
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars + P_READY + t);
     }
-    if (ok && rng.lo <= rng.hi) {
-      if (!__all_sync(0xffffffffu, mbar_wait(bars + O_DONE + t, 0))) { if (lane == 0) atomicExch(error, 13); ok = false; }
-      tc_fence_after();
-    }
-    if (ok && rng.lo <= rng.hi) {  // the whole warp reads tensor memory; rows past the end store nothing
-      const float inv = valid ? 1.0f / l : 0.f;
-      bf16* dst = out + (size_t)(row0 + tok) * HQ * D + (size_t)(kh * G + (valid ? R % G : 0)) * D;
+    // the row's sum is the two halves' sums; every thread comes here exactly once, whatever happened before
+    xsum[half * ROWS + r] = l[0];
+    xsum[2 * ROWS + half * ROWS + r] = l[1];
+    pair_sync();
+    l[0] += xsum[(half ^ 1) * ROWS + r];
+    l[1] += xsum[2 * ROWS + (half ^ 1) * ROWS + r];
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+    for (int t = 0; t < 2; ++t) {
+      if (!ok || rng[t].lo > rng[t].hi) continue;
+      if (!__all_sync(0xffffffffu, mbar_wait(bars + O_DONE + t, 0))) { if (lane == 0) atomicExch(error, 13); continue; }
+      tc_fence_after();
+      // the whole warp reads tensor memory; rows past the end store nothing. Each warp of a row writes half the columns.
+      const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
+      const int R = pair * PAIR + t * ROWS + r;
+      const float inv = valid[t] ? 1.0f / l[t] : 0.f;
+      bf16* dst = out + (size_t)(row0 + tok[t]) * HQ * D + (size_t)(kh * G + (valid[t] ? R % G : 0)) * D + half * (D / 2);
+#pragma unroll
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_o + c0, o);
+        tmem_ld_32x32(tmem_o + half * (D / 2) + c0, o);
         tmem_wait_ld();
-        if (valid) {
+        if (valid[t]) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             uint4 pk;
@@ -386,7 +421,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
-constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64 + PAGE_IDS * sizeof(int);
+constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + N_BARS * 8 + 64 + PAGE_IDS * sizeof(int) + 8 * ROWS * sizeof(float) + 16;
 
 }  // namespace
 
