@@ -3,8 +3,10 @@
 ``Kernels`` is the one object through which the engine computes. Every method
 launches this package's own kernels on torch's current CUDA stream; the only
 library routine on the path is the dense matrix product of many rows in
-bfloat16 (``torch.matmul``, i.e. cuBLAS), which is where the reference calls
-cuBLAS too (engine/model.py:295,299,301,303 of willzeng274/kernel-rush-kawk).
+bfloat16 (cuBLASLt, called by csrc/lt_gemm.cu with the algorithm picked by
+measurement; ``torch.matmul`` for layouts that it does not take), which is
+where the reference calls the library too (engine/model.py:295,299,301,303 of
+willzeng274/kernel-rush-kawk).
 There is no fallback: without a CUDA device and the compiled libraries,
 construction raises.
 """
@@ -46,6 +48,8 @@ _SIGNATURES = {
     "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_selftest_wait_runs_out": [_P, c_int, _P],
     "krk_skinny_linear": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
+    "krk_lt_gemm_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "krk_lt_gemm_report": [_P, _P],
 }
 _ATTN_SIGNATURES = {
     "krk_attention_simple": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
@@ -102,6 +106,7 @@ class Kernels:
         self._select_scratch = None
         self.use_tcgen05_attention = True
         self.use_tma_decode_attention = True
+        self.use_tuned_library_gemm = hasattr(self.core, "krk_lt_gemm_bf16")
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -275,7 +280,27 @@ class Kernels:
                     and w.data_ptr() % 16 == 0 and hasattr(self.core, "krk_gemm_tcgen05")):
                 return self.gemm_tcgen05(x, w, out_float32=True)
             return self._gemm_nt(x, w, out_dtype)
+        if (self.use_tuned_library_gemm and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+                and w.stride(0) % 8 == 0 and w.shape[0] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            return self._library_gemm(x, w)
         return torch.matmul(x, w.t())
+
+    def _library_gemm(self, x, w):
+        """The library's product with the algorithm picked by measurement (csrc/lt_gemm.cu)."""
+        M, K = x.shape
+        N = w.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        rc = self.core.krk_lt_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N, 1,
+                                        None, self._stream())
+        if rc:
+            raise KernelError(f"the library product of {M} x {N} x {K} failed with code {rc}")
+        return out
+
+    def library_gemm_report(self):
+        """(shape classes with a measured choice, how many of them kept the heuristic's first proposal)."""
+        a, b = c_int(0), c_int(0)
+        self.core.krk_lt_gemm_report(ctypes.byref(a), ctypes.byref(b))
+        return a.value, b.value
 
     def gate_up_swiglu(self, h, w_gate_up, intermediate):
         if self._use_skinny(h, w_gate_up):

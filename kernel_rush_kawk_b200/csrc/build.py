@@ -26,7 +26,8 @@ from pathlib import Path
 
 SRC_DIR = Path(__file__).parent
 
-CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu"]
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu", "lt_gemm.cu"]
+CORE_LIBS = ["-lcublasLt"]  # lt_gemm.cu; the process already holds the copy that torch loaded
 ATTN_SOURCES = ["attention_simple.cu", "attention_mma.cu", "attention_tcgen05.cu"]
 HEADERS = ["common.cuh", "mma.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 
@@ -80,7 +81,7 @@ def _key(sources, defines) -> str:
     for name in list(sources) + _existing(HEADERS):
         h.update(name.encode())
         h.update((SRC_DIR / name).read_bytes())
-    h.update(" ".join(NVCC_FLAGS + list(defines)).encode())
+    h.update(" ".join(NVCC_FLAGS + list(defines) + CORE_LIBS).encode())
     return h.hexdigest()[:12]
 
 
@@ -129,8 +130,12 @@ def build_library(kind: str, head_dim: int | None = None, verbose: bool = True) 
                 with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
                     list(pool.map(lambda so: _compile_one(nvcc, SRC_DIR / so[0], so[1], defines), zip(sources, objs)))
                 tmp = work / target.name
+                libs = []
+                if kind == "core":  # the library's directory as a run path too, should the process not hold a copy yet
+                    lib_dir = Path(nvcc).resolve().parent.parent / "lib64"
+                    libs = [f"-L{lib_dir}", *CORE_LIBS, "-Xlinker", f"-rpath={lib_dir}"]
                 r = subprocess.run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode",
-                                    "arch=compute_100a,code=sm_100a"], capture_output=True, text=True)
+                                    "arch=compute_100a,code=sm_100a", *libs], capture_output=True, text=True)
                 if r.returncode != 0:
                     raise BuildError(f"linking {target.name} failed:\n{r.stdout}\n{r.stderr}")
                 os.replace(tmp, target)

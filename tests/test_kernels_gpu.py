@@ -109,6 +109,44 @@ def test_few_row_products_that_split_k_over_a_cluster(ops, mnk):
         assert torch.equal(ops.linear(x, w), got), "the sum over the cluster's parts must not depend on timing"
 
 
+def test_library_gemm_with_measured_algorithm(ops):
+    """Products of more than 16 rows in bfloat16 go to the library with the algorithm picked by timing its
+    proposals: the first call of a shape class measures, later calls (other row counts of the class, a view
+    with a wider row stride, a stream capture) reuse the choice, and all of them give the plain product."""
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    assert ops.use_tuned_library_gemm
+    before, _ = ops.library_gemm_report()
+    w = rand((1096, 520), dtype, 91, 0.05)
+    for m in (17, 64, 300, 400, 512, 700):  # 300, 400 and 512 are one class, measured at 300
+        x = rand((m, 520), dtype, 92 + m)
+        close(ops.linear(x, w), ref.linear(x, w), dtype, f"library product, {m} rows")
+    after, _ = ops.library_gemm_report()
+    assert after - before == 4, "classes: 17, 64, 512 (300, 400, 512), 768 (700)"
+    wide = rand((300, 1040), dtype, 93)
+    x = wide[:, :520]  # rows 1,040 apart
+    close(ops.linear(x, w), ref.linear(x.contiguous(), w), dtype, "library product of a strided view")
+    ops.use_tuned_library_gemm = False
+    try:
+        other = ops.linear(x, w)
+    finally:
+        ops.use_tuned_library_gemm = True
+    close(ops.linear(x, w), other, dtype, "measured choice against the heuristic's")
+    # a class first met under capture runs the heuristic's first proposal and stays unmeasured
+    x = rand((33, 520), dtype, 94)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            y = ops.linear(x, w)
+        graph.replay()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    close(y, ref.linear(x, w), dtype, "library product in a captured graph")
+    assert ops.library_gemm_report()[0] == after + 1, "the strided view's class was measured, the captured one was not"
+
+
 @pytest.mark.parametrize("mnk", [(128, 128, 64), (128, 128, 512), (256, 384, 2560), (130, 200, 72), (77, 3000, 1000),
                                  (2048, 2560, 4096)])
 def test_tcgen05_gemm(ops, mnk):
