@@ -7,6 +7,9 @@
 // stream capture, every proposed algorithm is timed on the caller's own buffers and the fastest is
 // kept for the class; under capture, and for classes not yet timed, the heuristic's first choice runs.
 //
+// One workspace per device: products of one device are meant to run on one stream at a time, as the
+// engine's do. The first call on a device allocates it, so that call must not come under stream capture.
+//
 // A shape class is (rows rounded up to a multiple of 256, or the exact row count up to 256; N; K;
 // the leading dimensions). A plan (descriptors, the heuristic's proposals) is kept per exact shape.
 #include "common.cuh"
@@ -40,8 +43,15 @@ struct State {
   std::map<Shape, int> chosen_index;             // for reports: the proposal's index at the time it was chosen
 };
 
-State& state() {
-  static State s;
+// one state per device: a handle and its workspace belong to the device that was current when they were made
+State* state() {
+  static std::mutex mu;
+  static std::map<int, State*> by_device;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  State*& s = by_device[device];
+  if (!s) s = new State();  // lives as long as the process
   return s;
 }
 
@@ -83,18 +93,32 @@ int run(State& s, const Plan& p, const cublasLtMatmulAlgo_t& algo, const void* x
 KRK_API int krk_lt_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldw, int ldy, int tune,
                              int* picked, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  State& s = state();
+  State* sp = state();
+  if (!sp) return -20;
+  State& s = *sp;
   std::lock_guard<std::mutex> lock(s.mu);
   if (!s.handle) {
-    if (cublasLtCreate(&s.handle) != CUBLAS_STATUS_SUCCESS) return -20;
-    if (cudaMalloc(&s.workspace, WORKSPACE_BYTES) != cudaSuccess) return -20;
+    cublasLtHandle_t handle = nullptr;
+    if (cublasLtCreate(&handle) != CUBLAS_STATUS_SUCCESS) return -20;
+    if (cudaMalloc(&s.workspace, WORKSPACE_BYTES) != cudaSuccess) {
+      cublasLtDestroy(handle);
+      s.workspace = nullptr;
+      return -20;
+    }
+    s.handle = handle;
   }
   const Shape shape{M, N, K, ldx, ldw, ldy};
   auto it = s.plans.find(shape);
   if (it == s.plans.end()) {
     Plan p;
     const int rc = make_plan(s, p, M, N, K, ldx, ldw, ldy);
-    if (rc) return rc;
+    if (rc) {
+      if (p.op) cublasLtMatmulDescDestroy(p.op);
+      if (p.w) cublasLtMatrixLayoutDestroy(p.w);
+      if (p.x) cublasLtMatrixLayoutDestroy(p.x);
+      if (p.y) cublasLtMatrixLayoutDestroy(p.y);
+      return rc;
+    }
     it = s.plans.emplace(shape, std::move(p)).first;
   }
   const Plan& plan = it->second;
@@ -148,7 +172,9 @@ KRK_API int krk_lt_gemm_bf16(const void* x, const void* w, void* y, int M, int N
 
 // How many shape classes have a measured choice, and how many of them kept the heuristic's first proposal.
 KRK_API int krk_lt_gemm_report(int* classes, int* kept_first) {
-  State& s = state();
+  State* sp = state();
+  if (!sp) return -20;
+  State& s = *sp;
   std::lock_guard<std::mutex> lock(s.mu);
   *classes = (int)s.chosen.size();
   int first = 0;
