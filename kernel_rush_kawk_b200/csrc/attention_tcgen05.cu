@@ -85,7 +85,7 @@ __device__ __forceinline__ TileRange tile_range(int row_begin, int n_rows, int G
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                         const __grid_constant__ CUtensorMap map_q, int q_by_tma, bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
+                         const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_o, int q_by_tma, bf16* __restrict__ out, const bf16* __restrict__ qkv, int q_stride, int HQ, int HKV,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
                          int width, float scale_log2, int window, int* __restrict__ error) {
@@ -136,14 +136,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   auto load_v = [&](int i) { load_tile(v_s + (i & 1) * TILE_BYTES, &map_v, bars + V_FULL + (i & 1), i); };
 
   if (warp == 8) {
-    for (int i = lane; i < min(2 * n, PAGE_IDS); i += 32) pages_s[i] = table[(size_t)slot * width + (2 * j_lo + i) % width];
-    __syncwarp();
+    // The block's first loads in the order of what they wait for: the error word and the page-table entries are
+    // requested together, the query tiles (which need neither) go out before either has arrived.
+    // A block of this step that gave up on a wait (codes from 3 on): the others do no work. The host reads and
+    // clears the word at the end of every step, so a flag never outlives the step that raised it.
+    const int error_now = *reinterpret_cast<volatile int*>(error);
+    int page_here[PAGE_IDS / 32 > 4 ? 4 : PAGE_IDS / 32];  // the first 128 entries, one load per lane and round
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = lane + 32 * q;
+      page_here[q] = i < min(2 * n, PAGE_IDS) ? table[(size_t)slot * width + (2 * j_lo + i) % width] : 0;
+    }
     if (lane == 0) {
       for (int i = 0; i < N_BARS; ++i) mbar_init(bars + i, (i == P_READY || i == P_READY + 1) ? 2 * ROWS : 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      // a block of this step that gave up on a wait (codes from 3 on): the others do no work. The host reads and
-      // clears the word at the end of every step, so a flag never outlives the step that raised it.
-      tmem_slot[1] = (uint32_t)(*reinterpret_cast<volatile int*>(error) >= 3);
       for (int i = 0; i < 4; ++i) gave_up[i] = 0;
       if (q_by_tma) {
         // a query tile is a box of 128 / G tokens x G heads x 64 dims per 64-wide block of the head: its rows
@@ -155,6 +161,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           for (int h = 0; h < DB; ++h)
             tma_load_3d(q_s + t * TILE_BYTES + h * SUB, &map_q, bars + Q_FULL, h * 64, kh * G, row0 + (pair * PAIR + t * ROWS) / G);
       }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (lane + 32 * q < min(2 * n, PAGE_IDS)) pages_s[lane + 32 * q] = page_here[q];
+    for (int i = lane + 128; i < min(2 * n, PAGE_IDS); i += 32) pages_s[i] = table[(size_t)slot * width + (2 * j_lo + i) % width];
+    __syncwarp();
+    if (lane == 0) {
+      tmem_slot[1] = (uint32_t)(error_now >= 3);
       load_k(0);
       load_v(0);
       if (n > 1) load_k(1);
@@ -282,7 +296,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       lo[t] = (valid[t] && window > 0) ? max(0, pos[t] - window + 1) : 0;
     }
     auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
-    bool ok = true;
+    bool ok = true, stores_pending = false;
     uint32_t step = 0;
     for (int j = j_lo; j <= j_hi && ok; ++j) {
 #pragma unroll
@@ -385,20 +399,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     l[1] += xsum[2 * ROWS + (half ^ 1) * ROWS + r];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-      if (!ok || rng[t].lo > rng[t].hi) continue;
-      if (!__all_sync(0xffffffffu, mbar_wait(bars + O_DONE + t, 0))) { if (lane == 0) atomicExch(error, 13); continue; }
-      tc_fence_after();
-      // the whole warp reads tensor memory; rows past the end store nothing. Each warp of a row writes half the columns.
-      const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
-      const int R = pair * PAIR + t * ROWS + r;
-      const float inv = valid[t] ? 1.0f / l[t] : 0.f;
-      bf16* dst = out + (size_t)(row0 + tok[t]) * HQ * D + (size_t)(kh * G + (valid[t] ? R % G : 0)) * D + half * (D / 2);
+      if (rng[t].lo > rng[t].hi) continue;  // the same for every thread of the block
+      // O_t, divided by the row sums and rounded, goes through shared memory: a thread holds half a row, and rows
+      // are 2 * D bytes apart at best in the output. It is staged in the tile's query buffer, which its MMAs are
+      // done with, in the query tile's own layout (128-byte swizzle), and leaves as the query tile came: one
+      // tiled store per 64-wide block of the head when the tile is whole, else 16-byte pieces by all threads,
+      // consecutive threads storing consecutive pieces (the rows of a token lie side by side in the output).
+      const bool fine = ok && __all_sync(0xffffffffu, mbar_wait(bars + O_DONE + t, 0));
+      unsigned char* stage = q_s + t * TILE_BYTES;
+      if (fine) {
+        tc_fence_after();
+        const uint32_t tmem_o = tmem + TMEM_O + t * D + lane_addr;
+        const float inv = valid[t] ? 1.0f / l[t] : 0.f;
 #pragma unroll
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
-        uint32_t o[32];
-        tmem_ld_32x32(tmem_o + half * (D / 2) + c0, o);
-        tmem_wait_ld();
-        if (valid[t]) {
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_o + half * (D / 2) + c0, o);
+          tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             uint4 pk;
@@ -406,12 +423,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 #pragma unroll
             for (int e = 0; e < 4; ++e)
               pp[e] = __floats2bfloat162_rn(__uint_as_float(o[c + 2 * e]) * inv, __uint_as_float(o[c + 2 * e + 1]) * inv);
-            *reinterpret_cast<uint4*>(dst + c0 + c) = pk;
+            const int piece = (half * (D / 2) + c0 + c) / 8;
+            *reinterpret_cast<uint4*>(stage + (piece / 8) * SUB + swz(r, piece % 8)) = pk;
           }
         }
-        __syncwarp();
+        fence_async_smem();
+      } else if (lane == 0) {
+        if (ok) atomicExch(error, 13);
+        gave_up[quad] = 1;
+      }
+      asm volatile("bar.sync 5, 256;" ::: "memory");  // the eight softmax warps
+      if (gave_up[0] | gave_up[1] | gave_up[2] | gave_up[3]) continue;
+      const int row_begin = pair * PAIR + t * ROWS;
+      if (q_by_tma && row_begin + ROWS <= n_rows) {
+        if (threadIdx.x == 0) {
+#pragma unroll
+          for (int h = 0; h < DB; ++h) tma_store_3d(&map_o, stage + h * SUB, h * 64, kh * G, row0 + row_begin / G);
+          tma_store_commit();
+          stores_pending = true;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < ROWS * (D / 8) / 256; ++k) {
+          const int p = threadIdx.x + 256 * k;
+          const int row = p / (D / 8), piece = p % (D / 8);
+          const int R = row_begin + row;
+          if (R < n_rows)
+            *reinterpret_cast<uint4*>(out + (size_t)(row0 + R / G) * HQ * D + (size_t)(kh * G + R % G) * D + piece * 8) =
+                *reinterpret_cast<const uint4*>(stage + (piece / 8) * SUB + swz(row, piece % 8));
+        }
       }
     }
+    if (stores_pending) tma_store_wait_read();  // shared memory is given up when the block ends
   }
   tc_fence_before();
   __syncthreads();
@@ -450,6 +493,11 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
     rc = make_map_bf16_3d(&map_q, qkv, D, HQ, total_rows, D, q_stride, G, ROWS / G);
     if (rc) return rc;
   }
+  CUtensorMap map_o = map_k;
+  if (q_by_tma) {
+    rc = make_map_bf16_3d(&map_o, out, D, HQ, total_rows, D, (long long)HQ * D, G, ROWS / G);
+    if (rc) return rc;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
@@ -458,7 +506,7 @@ KRK_API int krk_attention_prefill_tcgen05(void* out, const void* qkv, int q_stri
   }
   dim3 grid((unsigned)(tiles * HKV), n_seqs, 1);
   attention_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
-      map_k, map_v, map_q, q_by_tma, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
+      map_k, map_v, map_q, map_o, q_by_tma, (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
       scale * LOG2E, window, error);
   KRK_CHECK_LAUNCH();
   return 0;

@@ -59,6 +59,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// A tiled store from shared memory (written by threads: fence_async_smem() and a barrier first) and the wait for
+// the stores of this thread to have read their source, after which the shared memory may be reused or given up.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
 // start address, stride between 8-row groups = 1024 bytes, descriptor version 1, swizzle mode 2.
 __device__ __forceinline__ uint64_t umma_desc(const void* smem_tile) {
