@@ -789,6 +789,21 @@ int launch_decode_fused(bf16* out, const bf16* qkv, int q_stride, int HQ, int HK
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
+  if (splits > 8) {
+    // Clusters of more than eight blocks have to be allowed per kernel, and a device (or a partition of one) need
+    // not have room for one: asked once, with this launch's shape; -8 tells the caller to take eight.
+    static int fits = -1;
+    if (fits < 0) {
+      int clusters = 0;
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess ||
+          cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        clusters = 0;
+      }
+      fits = clusters > 0 ? 1 : 0;
+    }
+    if (!fits) return -8;
+  }
   return (int)cudaLaunchKernelEx(&cfg, kern, out, qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, cos_t, sin_t, eps,
                                  seq_slot, seq_start, table, width, k_cache, v_cache, scale * LOG2E, window, row_tiles,
                                  n_pos, inbox_rows, error);
@@ -1120,7 +1135,7 @@ KRK_API int krk_trace_dump(unsigned long long* host, unsigned int cap, unsigned 
 
 // One token per sequence, from the raw QKV rows to the attention output in one launch (see the
 // kernel's text). qkv rows hold q heads, k heads, v heads; gains and tables may be null. splits:
-// 1, 2, 4 or 8 blocks per cluster. The keys and values of the new tokens are written to the cache.
+// 1, 2, 4, 8 or 16 blocks per cluster (16 where the device has room for such a cluster, else 8). The keys and values of the new tokens are written to the cache.
 KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride, int HQ, int HKV, const void* q_gain,
                                        const void* k_gain, int gain_f32, const void* cos_t, const void* sin_t,
                                        float eps, const int* seq_slot, const int* seq_start, const int* table,
@@ -1130,7 +1145,14 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
   const int G = HQ / HKV;
   const int row_tiles = (G + 15) / 16;
   if (HKV * row_tiles > 65535 || n_seqs > 65535) return -3;
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -2;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -2;
+  if (splits == 16) {
+    const int rc = launch_decode_fused<2>((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32,
+                                          (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot, seq_start, table, width,
+                                          (bf16*)k_cache, (bf16*)v_cache, n_seqs, scale, window, splits, n_pos, error, stream);
+    if (rc != -8) return rc;
+    splits = 8;  // no room for a cluster of sixteen on this device
+  }
   if (splits == 1)
     return launch_decode_fused<3>((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32,
                                   (const bf16*)cos_t, (const bf16*)sin_t, eps, seq_slot, seq_start, table, width,

@@ -329,10 +329,13 @@ class Kernels:
             out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
             row_tiles = -(-(heads // cache.kv_heads) // 16)
             # key splits (blocks per cluster) by the number of (sequence, kv head, row tile) items alone,
-            # never by lengths, so a captured step stays valid; measured best on B200 at 1, 8, 16 and 32 or 64
-            # sequences of the 4B shape: 8, 4, 2 and 1 (one block per item runs a deeper page pipeline)
+            # never by lengths, so a captured step stays valid; measured best on B200 at 1, 2 to 4, 8, 16 and 32 or
+            # 64 sequences of the 4B shape: 16, 8, 4, 2 and 1 (one block per item runs a deeper page pipeline). One
+            # sequence has eight items: sixteen splits are 128 blocks where eight are 64, and what bounds the
+            # kernel is the bytes its blocks have in flight (one step of the 4B shape at 32,000 tokens of context:
+            # 4.41 -> 3.14 ms, at 8,000: 2.51 -> 2.17, at 1,000: 1.93 -> 1.91; at two sequences sixteen gain nothing)
             items = n * cache.kv_heads * row_tiles
-            splits = 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 192 else 1
+            splits = 16 if items <= 9 else 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 192 else 1
             gain = q_gain if q_gain is not None else k_gain
             n_pos = cos.shape[0] if cos is not None else 0x7fffffff
             if (splits == 1 and self.use_tma_decode_attention and head_dim % 64 == 0 and cache.width <= 1024
