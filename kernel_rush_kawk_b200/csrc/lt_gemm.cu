@@ -10,8 +10,10 @@
 // One workspace per device: products of one device are meant to run on one stream at a time, as the
 // engine's do. The first call on a device allocates it, so that call must not come under stream capture.
 //
-// A shape class is (rows rounded up to a multiple of 256, or the exact row count up to 256; N; K;
-// the leading dimensions). A plan (descriptors, the heuristic's proposals) is kept per exact shape.
+// A shape class is (the row count up to 256 rows, its next multiple of 256 up to 2,048, its next power of
+// two beyond; N; K; the leading dimensions): a serving process meets a bounded number of classes, and a
+// class is measured on 4,096 rows at most. A plan (descriptors, the heuristic's proposals) is kept per
+// exact shape.
 #include "common.cuh"
 
 #include <cublasLt.h>
@@ -34,13 +36,18 @@ struct Plan {
   std::vector<cublasLtMatmulHeuristicResult_t> proposals;
 };
 
+struct Choice {
+  cublasLtMatmulAlgo_t algo;
+  int index;  // among the proposals for `rows` rows
+  int rows;   // the row count it was measured on
+};
+
 struct State {
   std::mutex mu;
   cublasLtHandle_t handle = nullptr;
   void* workspace = nullptr;
   std::map<Shape, Plan> plans;
-  std::map<Shape, cublasLtMatmulAlgo_t> chosen;  // by shape class
-  std::map<Shape, int> chosen_index;             // for reports: the proposal's index at the time it was chosen
+  std::map<Shape, Choice> chosen;  // by shape class
 };
 
 // one state per device: a handle and its workspace belong to the device that was current when they were made
@@ -55,7 +62,17 @@ State* state() {
   return s;
 }
 
-int row_class(int M) { return M <= 256 ? M : (M + 255) / 256 * 256; }
+constexpr int MEASURED_ROWS = 4096;
+constexpr size_t MAX_PLANS = 4096;
+
+// exact up to 256 rows (decode batch sizes), multiples of 256 up to 2,048, powers of two beyond
+int row_class(int M) {
+  if (M <= 256) return M;
+  if (M <= 2048) return (M + 255) / 256 * 256;
+  int c = 4096;
+  while (c < M && c < (1 << 30)) c *= 2;
+  return c;
+}
 
 // In column-major terms: y^T [N x M] = op_T(W as K x N, ld = ldw) * (x as K x M, ld = ldx)
 int make_plan(State& s, Plan& p, int M, int N, int K, int ldx, int ldw, int ldy) {
@@ -79,6 +96,26 @@ int make_plan(State& s, Plan& p, int M, int N, int K, int ldx, int ldw, int ldy)
   return 0;
 }
 
+// the plan of an exact shape, made at its first use
+int plan_for(State& s, int M, int N, int K, int ldx, int ldw, int ldy, const Plan** out) {
+  const Shape shape{M, N, K, ldx, ldw, ldy};
+  auto it = s.plans.find(shape);
+  if (it == s.plans.end()) {
+    Plan p;
+    const int rc = make_plan(s, p, M, N, K, ldx, ldw, ldy);
+    if (rc) {
+      if (p.op) cublasLtMatmulDescDestroy(p.op);
+      if (p.w) cublasLtMatrixLayoutDestroy(p.w);
+      if (p.x) cublasLtMatrixLayoutDestroy(p.x);
+      if (p.y) cublasLtMatrixLayoutDestroy(p.y);
+      return rc;
+    }
+    it = s.plans.emplace(shape, std::move(p)).first;
+  }
+  *out = &it->second;
+  return 0;
+}
+
 int run(State& s, const Plan& p, const cublasLtMatmulAlgo_t& algo, const void* x, const void* w, void* y, cudaStream_t stream) {
   const float one = 1.f, zero = 0.f;
   const cublasStatus_t st = cublasLtMatmul(s.handle, p.op, &one, w, p.w, x, p.x, &zero, y, p.y, y, p.y, &algo, s.workspace, WORKSPACE_BYTES, stream);
@@ -89,7 +126,7 @@ int run(State& s, const Plan& p, const cublasLtMatmulAlgo_t& algo, const void* x
 
 // tune != 0: time the proposals if this shape class has none chosen yet and the stream is not capturing.
 // Returns 0, or a negative code; *picked (may be null) receives the index of the proposal that ran, -1 if
-// the algorithm came from another shape of the class.
+// the algorithm was measured on another row count.
 KRK_API int krk_lt_gemm_bf16(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldw, int ldy, int tune,
                              int* picked, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -107,67 +144,71 @@ KRK_API int krk_lt_gemm_bf16(const void* x, const void* w, void* y, int M, int N
     }
     s.handle = handle;
   }
-  const Shape shape{M, N, K, ldx, ldw, ldy};
-  auto it = s.plans.find(shape);
-  if (it == s.plans.end()) {
-    Plan p;
-    const int rc = make_plan(s, p, M, N, K, ldx, ldw, ldy);
-    if (rc) {
-      if (p.op) cublasLtMatmulDescDestroy(p.op);
-      if (p.w) cublasLtMatrixLayoutDestroy(p.w);
-      if (p.x) cublasLtMatrixLayoutDestroy(p.x);
-      if (p.y) cublasLtMatrixLayoutDestroy(p.y);
-      return rc;
+  if (s.plans.size() > MAX_PLANS) {  // a process that has met this many row counts starts its list over
+    for (auto& kv : s.plans) {
+      cublasLtMatmulDescDestroy(kv.second.op);
+      cublasLtMatrixLayoutDestroy(kv.second.w);
+      cublasLtMatrixLayoutDestroy(kv.second.x);
+      cublasLtMatrixLayoutDestroy(kv.second.y);
     }
-    it = s.plans.emplace(shape, std::move(p)).first;
+    s.plans.clear();
   }
-  const Plan& plan = it->second;
+  const Plan* plan = nullptr;
+  int rc = plan_for(s, M, N, K, ldx, ldw, ldy, &plan);
+  if (rc) return rc;
   const Shape cls{row_class(M), N, K, ldx, ldw, ldy};
   auto chosen = s.chosen.find(cls);
-  if (chosen != s.chosen.end()) {
-    // an algorithm timed on another row count of the class: use it if the library accepts it for this one
-    cublasLtMatmulHeuristicResult_t check;
-    if (cublasLtMatmulAlgoCheck(s.handle, plan.op, plan.w, plan.x, plan.y, plan.y, &chosen->second, &check) == CUBLAS_STATUS_SUCCESS &&
-        check.workspaceSize <= WORKSPACE_BYTES) {
-      if (picked) *picked = row_class(M) == M ? s.chosen_index[cls] : -1;
-      return run(s, plan, chosen->second, x, w, y, stream);
+  if (chosen == s.chosen.end()) {
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(stream, &capturing);
+    if (!tune || capturing != cudaStreamCaptureStatusNone) {
+      if (picked) *picked = 0;
+      return run(s, *plan, plan->proposals[0].algo, x, w, y, stream);
     }
-    if (picked) *picked = 0;
-    return run(s, plan, plan.proposals[0].algo, x, w, y, stream);
-  }
-  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-  cudaStreamIsCapturing(stream, &capturing);
-  if (!tune || capturing != cudaStreamCaptureStatusNone || plan.proposals.size() == 1) {
-    if (picked) *picked = 0;
-    return run(s, plan, plan.proposals[0].algo, x, w, y, stream);
-  }
-  // time every proposal: one warm-up run and the fastest of three timed ones, on the caller's stream and buffers
-  cudaEvent_t e0, e1;
-  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return -26;
-  int best = 0;
-  float best_ms = 1e30f;
-  for (int a = 0; a < (int)plan.proposals.size(); ++a) {
-    if (plan.proposals[a].state != CUBLAS_STATUS_SUCCESS || plan.proposals[a].workspaceSize > WORKSPACE_BYTES) continue;
-    if (run(s, plan, plan.proposals[a].algo, x, w, y, stream)) continue;
-    float fastest = 1e30f;
-    bool ok = true;
-    for (int rep = 0; rep < 3 && ok; ++rep) {
-      cudaEventRecord(e0, stream);
-      ok = run(s, plan, plan.proposals[a].algo, x, w, y, stream) == 0;
-      cudaEventRecord(e1, stream);
-      if (cudaEventSynchronize(e1) != cudaSuccess) { cudaEventDestroy(e0); cudaEventDestroy(e1); return -27; }
-      float ms = 0.f;
-      cudaEventElapsedTime(&ms, e0, e1);
-      fastest = ms < fastest ? ms : fastest;
+    // Time every proposal on the caller's stream and buffers: one warm-up run and the faster of two timed ones.
+    // Long steps are measured on their first MEASURED_ROWS rows, so that a new class costs a bounded time
+    // (the runs write into y, which the real product then overwrites).
+    const int rows = M < MEASURED_ROWS ? M : MEASURED_ROWS;
+    const Plan* trial = plan;
+    if (rows != M && (rc = plan_for(s, rows, N, K, ldx, ldw, ldy, &trial))) return rc;
+    cudaEvent_t e0, e1;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return -26;
+    int best = 0;
+    float best_ms = 1e30f;
+    for (int a = 0; a < (int)trial->proposals.size(); ++a) {
+      if (trial->proposals[a].state != CUBLAS_STATUS_SUCCESS || trial->proposals[a].workspaceSize > WORKSPACE_BYTES) continue;
+      if (run(s, *trial, trial->proposals[a].algo, x, w, y, stream)) continue;
+      float fastest = 1e30f;
+      bool ok = true;
+      for (int rep = 0; rep < 2 && ok; ++rep) {
+        cudaEventRecord(e0, stream);
+        ok = run(s, *trial, trial->proposals[a].algo, x, w, y, stream) == 0;
+        cudaEventRecord(e1, stream);
+        if (cudaEventSynchronize(e1) != cudaSuccess) { cudaEventDestroy(e0); cudaEventDestroy(e1); return -27; }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        fastest = ms < fastest ? ms : fastest;
+      }
+      if (ok && fastest < best_ms) { best_ms = fastest; best = a; }
     }
-    if (ok && fastest < best_ms) { best_ms = fastest; best = a; }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    chosen = s.chosen.emplace(cls, Choice{trial->proposals[best].algo, best, rows}).first;
   }
-  cudaEventDestroy(e0);
-  cudaEventDestroy(e1);
-  s.chosen[cls] = plan.proposals[best].algo;
-  s.chosen_index[cls] = best;
-  if (picked) *picked = best;
-  return run(s, plan, plan.proposals[best].algo, x, w, y, stream);
+  // an algorithm measured on another row count runs if the library accepts it for this one
+  const Choice& c = chosen->second;
+  if (c.rows == M) {
+    if (picked) *picked = c.index;
+    return run(s, *plan, c.algo, x, w, y, stream);
+  }
+  cublasLtMatmulHeuristicResult_t check;
+  if (cublasLtMatmulAlgoCheck(s.handle, plan->op, plan->w, plan->x, plan->y, plan->y, &c.algo, &check) == CUBLAS_STATUS_SUCCESS &&
+      check.workspaceSize <= WORKSPACE_BYTES) {
+    if (picked) *picked = -1;
+    return run(s, *plan, c.algo, x, w, y, stream);
+  }
+  if (picked) *picked = 0;
+  return run(s, *plan, plan->proposals[0].algo, x, w, y, stream);
 }
 
 // How many shape classes have a measured choice, and how many of them kept the heuristic's first proposal.
@@ -178,7 +219,7 @@ KRK_API int krk_lt_gemm_report(int* classes, int* kept_first) {
   std::lock_guard<std::mutex> lock(s.mu);
   *classes = (int)s.chosen.size();
   int first = 0;
-  for (const auto& kv : s.chosen_index) first += kv.second == 0;
+  for (const auto& kv : s.chosen) first += kv.second.index == 0;
   *kept_first = first;
   return 0;
 }

@@ -118,11 +118,12 @@ def test_library_gemm_with_measured_algorithm(ops):
     assert ops.use_tuned_library_gemm
     before, _ = ops.library_gemm_report()
     w = rand((1096, 520), dtype, 91, 0.05)
-    for m in (17, 64, 300, 400, 512, 700):  # 300, 400 and 512 are one class, measured at 300
+    # 300, 400 and 512 are one class, measured at 300; 4,500 and 6,000 are one, measured on the first 4,096 rows
+    for m in (17, 64, 300, 400, 512, 700, 4500, 6000):
         x = rand((m, 520), dtype, 92 + m)
         close(ops.linear(x, w), ref.linear(x, w), dtype, f"library product, {m} rows")
     after, _ = ops.library_gemm_report()
-    assert after - before == 4, "classes: 17, 64, 512 (300, 400, 512), 768 (700)"
+    assert after - before == 5, "classes: 17, 64, 512 (300, 400, 512), 768 (700), 8192 (4500, 6000)"
     wide = rand((300, 1040), dtype, 93)
     x = wide[:, :520]  # rows 1,040 apart
     close(ops.linear(x, w), ref.linear(x.contiguous(), w), dtype, "library product of a strided view")
