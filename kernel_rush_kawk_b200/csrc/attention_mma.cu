@@ -838,7 +838,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                             const int* __restrict__ table, int width, bf16* __restrict__ k_cache,
                             bf16* __restrict__ v_cache, float scale_log2, int window, int row_tiles, int n_pos, int ring,
-                            int* __restrict__ error) {
+                            int inbox_rows, int* __restrict__ error) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   bf16* units = reinterpret_cast<bf16*>(base);                                // [ring][UNIT_ELEMS], later the partials
@@ -846,8 +846,17 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   bf16* kv_new = q_s + 16 * DP;                                               // [2][D] the new token's key and value
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(kv_new + 2 * D);           // [ring]
   uint64_t* empty_bar = full_bar + ring;                                      // [ring]
-  int* pages = reinterpret_cast<int*>(empty_bar + ring);                      // [key blocks of this sequence]
+  int* pages = reinterpret_cast<int*>(empty_bar + ring);                      // [width] this block's key blocks
+  float* inbox = reinterpret_cast<float*>(pages + ((width + 3) & ~3));        // [splits][inbox_rows][D + 2], used in block 0
 
+  // The key blocks of a (sequence, kv head, row tile) may be split over the blocks of a thread-block cluster
+  // (few sequences, long contexts: more blocks, each with a ring of its own in flight); the partials meet in
+  // block 0's shared memory as in attention_decode_fused_kernel. "I have started" is waited for only before the
+  // first write into another block's shared memory.
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int n_splits = cluster.num_blocks(), split = cluster.block_rank();
+  if (n_splits > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   grid_launch_dependents();
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y % row_tiles;
   const int seq = blockIdx.z;
@@ -862,9 +871,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     pos = max(0, min(pos, n_pos - 1));
   }
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int j_first = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
-  const int n_blocks = j_last - j_first + 1;
+  const int j_all = lo / KRK_PAGE, j_last = pos / KRK_PAGE;
+  const int per = (j_last - j_all + 1 + n_splits - 1) / n_splits;
+  const int j_first = j_all + split * per, j_end = min(j_last, j_first + per - 1);  // this block's key blocks; none if j_first > j_end
+  const int n_blocks = max(0, j_end - j_first + 1);
   const int n_units = 2 * n_blocks;
+  const bool owns_new = n_blocks > 0 && j_end == j_last;  // this block's keys include the new token's
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < ring; ++r) {
@@ -894,6 +906,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         for (int h = 0; h < D / 64; ++h) tc::tma_load_2d(dst + h * SUB_ELEMS, map, full_bar + r, h * 64, row);
       }
     }
+    if (n_splits == 1) return;
+    // a split block's producer stays for the cluster's barriers, which count every thread
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    cluster.sync();
     return;
   }
 
@@ -944,7 +960,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (d < D) kv_new[D + d] = __float2bfloat16_rn(v_regs[i]);
     }
     __syncwarp();
-    if (rt == 0) {
+    if (rt == 0 && owns_new) {
       const int page = table[(size_t)slot * width + j_last % width];
       const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
       for (int d = lane; d < D; d += 32) {
@@ -976,7 +992,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (lane == 0) tc::mbar_arrive(empty_bar + u % ring);
   };
   const int tid = threadIdx.x;  // 0..127 among the consumers
-  for (int j = j_first; j <= j_last; ++j) {
+  for (int j = j_first; j <= j_end; ++j) {
     const int uk = 2 * (j - j_first), uv = uk + 1;
     bf16* ks = units + (size_t)(uk % ring) * UNIT_ELEMS;
     bf16* vs = units + (size_t)(uv % ring) * UNIT_ELEMS;
@@ -1020,7 +1036,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   }
   consumer_sync();
-  for (int r = warp; r < q_rows; r += 4) {  // the four warps' partials of a row, in warp order
+  // the four warps' partials of a row, in warp order: straight to the output if the block has all keys, else into
+  // block 0's inbox through distributed shared memory
+  float* inbox0 = n_splits > 1 ? cluster.map_shared_rank(inbox, 0) : nullptr;
+  if (n_splits > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block has started
+  for (int r = warp; r < q_rows; r += 4) {
     float mw[4], big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) { mw[w] = red[((size_t)w * 16 + r) * RP + D]; big = fmaxf(big, mw[w]); }
@@ -1028,13 +1048,54 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     float wgt[4], lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
-    const float inv = 1.0f / lsum;
-    bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
-    for (int d = lane; d < D; d += 32) {
-      float acc = 0.f;
+    if (n_splits == 1) {
+      const float inv = 1.0f / lsum;
+      bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
+      for (int d = lane; d < D; d += 32) {
+        float acc = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
-      dst[d] = __float2bfloat16_rn(acc * inv);
+        for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+        dst[d] = __float2bfloat16_rn(acc * inv);
+      }
+    } else {
+      float* dst = inbox0 + ((size_t)split * inbox_rows + r) * RP;
+      for (int d = lane; d < D; d += 32) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+        dst[d] = acc;
+      }
+      if (lane == 0) { dst[D] = big; dst[D + 1] = lsum; }
+    }
+  }
+  if (n_splits == 1) return;
+  cluster.sync();  // every block's partial has arrived in block 0
+  if (split == 0) {
+    for (int r = warp; r < q_rows; r += 4) {  // the splits' partials of a row, in split order
+      const float* mine = inbox + (size_t)r * RP;
+      const size_t step = (size_t)inbox_rows * RP;
+      float big = -INFINITY;
+      for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, mine[s2 * step + D]);
+      float lsum = 0.f;
+      float acc[(D + 31) / 32];
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+      for (int s2 = 0; s2 < n_splits; ++s2) {
+        const float w = exp2f(mine[s2 * step + D] - big);
+        lsum += w * mine[s2 * step + D + 1];
+#pragma unroll
+        for (int i = 0; i < (D + 31) / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) acc[i] += w * mine[s2 * step + d];
+        }
+      }
+      const float inv = 1.0f / lsum;
+      bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+      }
     }
   }
 }
@@ -1042,13 +1103,28 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 int launch_decode_tma(bf16* out, const bf16* qkv, int q_stride, int HQ, int HKV, const void* q_gain, const void* k_gain,
                       int gain_f32, const bf16* cos_t, const bf16* sin_t, float eps, const int* seq_slot,
                       const int* seq_start, const int* table, int width, bf16* k_cache, bf16* v_cache, int n_pages,
-                      int n_seqs, float scale, int window, int n_pos, int* error, cudaStream_t stream) {
+                      int n_seqs, float scale, int window, int splits, int n_pos, int* error, cudaStream_t stream) {
   if (width > TMA_MAX_WIDTH) return -2;
   const int G = HQ / HKV;
   const int row_tiles = (G + 15) / 16;
-  const size_t fixed = 1024 + (size_t)(16 * DP + 2 * D) * sizeof(bf16) + (size_t)width * sizeof(int) + 64;
-  // two blocks per SM: the ring takes what half of an SM's shared memory leaves
-  int ring = (int)((111 * 1024 - fixed) / UNIT_BYTES);
+  const int inbox_rows = G < 16 ? G : 16;
+  const size_t inbox = splits > 1 ? (size_t)splits * inbox_rows * (D + 2) * sizeof(float) : 0;
+  const size_t fixed = 1024 + (size_t)(16 * DP + 2 * D) * sizeof(bf16) + (size_t)((width + 3) & ~3) * sizeof(int) + 64 + inbox;
+  // The ring takes what the blocks that share an SM leave one another: two blocks per SM when there are more
+  // blocks than SMs, else one block with a ring of up to twelve units (bytes in flight are what bounds the kernel).
+  int sms = 148;
+  {
+    static int sm_count = 0;
+    if (!sm_count) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sm_count = 148;
+    }
+    sms = sm_count;
+  }
+  const long long blocks = (long long)splits * HKV * row_tiles * n_seqs;
+  const size_t budget = blocks > sms ? 111 * 1024 : 220 * 1024;
+  if (fixed + 2 * UNIT_BYTES > budget) return -2;
+  int ring = (int)((budget - fixed) / (UNIT_BYTES + 16));
   ring = ring > 12 ? 12 : ring;
   if (ring < 2 || (size_t)ring * UNIT_BYTES < (size_t)4 * 16 * (D + 2) * sizeof(float)) return -2;
   const size_t smem = fixed + (size_t)ring * UNIT_BYTES + (size_t)2 * ring * 8;
@@ -1064,9 +1140,41 @@ int launch_decode_tma(bf16* out, const bf16* qkv, int q_stride, int HQ, int HKV,
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  return (int)launch_pdl(attention_decode_tma_kernel, dim3(1, HKV * row_tiles, n_seqs), dim3(TMA_THREADS), smem, stream,
-                         map_k, map_v, out, qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, cos_t, sin_t, eps, seq_slot,
-                         seq_start, table, width, k_cache, v_cache, scale * LOG2E, window, row_tiles, n_pos, ring, error);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, HKV * row_tiles, n_seqs);
+  cfg.blockDim = dim3(TMA_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = splits;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  if (splits > 8) {
+    // clusters of more than eight blocks have to be allowed per kernel, and a device need not have room for one:
+    // asked once per shared-memory size; -8 tells the caller to take eight
+    static int fits = -1;
+    static size_t fits_smem = 0;
+    if (fits < 0 || fits_smem != smem) {
+      int clusters = 0;
+      if (cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess ||
+          cudaOccupancyMaxActiveClusters(&clusters, attention_decode_tma_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        clusters = 0;
+      }
+      fits = clusters > 0 ? 1 : 0;
+      fits_smem = smem;
+    }
+    if (!fits) return -8;
+  }
+  const float scale_log2 = scale * LOG2E;
+  return (int)cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel, map_k, map_v, out, qkv, q_stride, HQ, HKV, q_gain, k_gain,
+                                 gain_f32, cos_t, sin_t, eps, seq_slot, seq_start, table, width, k_cache, v_cache, scale_log2,
+                                 window, row_tiles, n_pos, ring, inbox_rows, error);
 }
 #endif  // head sizes that TMA pages serve
 
@@ -1162,22 +1270,29 @@ KRK_API int krk_attention_decode_fused(void* out, const void* qkv, int q_stride,
                                 (bf16*)k_cache, (bf16*)v_cache, n_seqs, scale, window, splits, n_pos, error, stream);
 }
 
-// The same step with one block per (sequence, kv head) fed by TMA (see attention_decode_tma_kernel): for many
-// sequences, where no key split is wanted. n_pages: pages of the cache (for the TMA maps). Returns -2 for head
-// sizes that are no multiple of 64 or page tables wider than 1024 entries: the caller then takes the kernel above.
+// The same step with the blocks fed by TMA (see attention_decode_tma_kernel): one block per (sequence, kv head),
+// or a cluster of `splits` blocks (1, 2, 4, 8 or 16; 8 where the device has no room for 16) that share its keys.
+// n_pages: pages of the cache (for the TMA maps). Returns -2 for head sizes that are no multiple of 64, page
+// tables wider than 1024 entries and shapes whose shared memory does not fit: the caller then takes the kernel above.
 KRK_API int krk_attention_decode_fused_tma(void* out, const void* qkv, int q_stride, int HQ, int HKV, const void* q_gain,
                                            const void* k_gain, int gain_f32, const void* cos_t, const void* sin_t,
                                            float eps, const int* seq_slot, const int* seq_start, const int* table,
                                            int width, void* k_cache, void* v_cache, int n_pages, int n_seqs, float scale,
-                                           int window, int n_pos, int* error, cudaStream_t stream) {
+                                           int window, int splits, int n_pos, int* error, cudaStream_t stream) {
 #if KRK_HEAD_DIM % 64 == 0
   if (n_seqs == 0) return 0;
   const int G = HQ / HKV;
   const int row_tiles = (G + 15) / 16;
   if (HKV * row_tiles > 65535 || n_seqs > 65535) return -3;
-  return launch_decode_tma((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, (const bf16*)cos_t,
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -2;
+  int rc = launch_decode_tma((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, (const bf16*)cos_t,
+                             (const bf16*)sin_t, eps, seq_slot, seq_start, table, width, (bf16*)k_cache, (bf16*)v_cache,
+                             n_pages, n_seqs, scale, window, splits, n_pos, error, stream);
+  if (rc == -8)  // no room for a cluster of sixteen on this device
+    rc = launch_decode_tma((bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, (const bf16*)cos_t,
                            (const bf16*)sin_t, eps, seq_slot, seq_start, table, width, (bf16*)k_cache, (bf16*)v_cache,
-                           n_pages, n_seqs, scale, window, n_pos, error, stream);
+                           n_pages, n_seqs, scale, window, 8, n_pos, error, stream);
+  return rc;
 #else
   return -2;
 #endif

@@ -63,7 +63,7 @@ _ATTN_SIGNATURES = {
     "krk_attention_decode_fused": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
                                    _P, c_int, c_float, c_int, c_int, c_int, _P, _P],
     "krk_attention_decode_fused_tma": [_P, _P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, c_float, _P, _P, _P, c_int, _P,
-                                       _P, c_int, c_int, c_float, c_int, c_int, _P, _P],
+                                       _P, c_int, c_int, c_float, c_int, c_int, c_int, _P, _P],
 }
 
 
@@ -106,6 +106,11 @@ class Kernels:
         self._select_scratch = None
         self.use_tcgen05_attention = True
         self.use_tma_decode_attention = True
+        # Key-split counts that take the TMA-fed single-token attention. It splits keys over a cluster like the
+        # cp.async kernel, bit for bit; measured on the 4B shape it wins with one block or two per item (16 sequences
+        # at 8,000 tokens of context: 4.95 against 5.53 ms a step) and loses with more (one sequence at 32,000
+        # tokens: 4.08 against 3.14 ms), where a block's own pace, not the bytes in flight, is the bound.
+        self.tma_decode_splits = {1, 2}
         self.use_tuned_library_gemm = hasattr(self.core, "krk_lt_gemm_bf16")
         self.launches = 0
 
@@ -338,16 +343,18 @@ class Kernels:
             splits = 16 if items <= 9 else 8 if items <= 37 else 4 if items <= 74 else 2 if items <= 192 else 1
             gain = q_gain if q_gain is not None else k_gain
             n_pos = cos.shape[0] if cos is not None else 0x7fffffff
-            if (splits == 1 and self.use_tma_decode_attention and head_dim % 64 == 0 and cache.width <= 1024
-                    and hasattr(lib, "krk_attention_decode_fused_tma")):
-                # many sequences: one block per (sequence, kv head), pages by TMA into a ring of half page-pairs
-                self._ok(lib.krk_attention_decode_fused_tma(
+            if (splits in self.tma_decode_splits and self.use_tma_decode_attention and head_dim % 64 == 0
+                    and cache.width <= 1024 and hasattr(lib, "krk_attention_decode_fused_tma")):
+                # many sequences: one block or two per (sequence, kv head), pages by TMA into a ring of half page-pairs
+                rc = lib.krk_attention_decode_fused_tma(
                     out.data_ptr(), qkv.data_ptr(), qkv.stride(0), heads, cache.kv_heads, _ptr(q_gain), _ptr(k_gain),
                     int(gain is not None and gain.dtype == torch.float32), _ptr(cos), _ptr(sin), eps,
                     batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
-                    cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], n, scale, int(window or 0), n_pos,
-                    self.error.data_ptr(), self._stream()), "fused decode attention (TMA)")
-                return out
+                    cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0], n, scale, int(window or 0), splits, n_pos,
+                    self.error.data_ptr(), self._stream())
+                if rc != -2:  # -2: the shapes do not fit this kernel's shared memory; the kernel below takes them
+                    self._ok(rc, "fused decode attention (TMA)")
+                    return out
             self._ok(lib.krk_attention_decode_fused(
                 out.data_ptr(), qkv.data_ptr(), qkv.stride(0), heads, cache.kv_heads, _ptr(q_gain), _ptr(k_gain),
                 int(gain is not None and gain.dtype == torch.float32), _ptr(cos), _ptr(sin), eps,

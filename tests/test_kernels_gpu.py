@@ -424,6 +424,51 @@ def test_tma_fed_decode_attention_equals_the_cp_async_kernel(ops, shape, window)
         assert torch.equal(a, b), f"{what} differ between the TMA-fed and the cp.async kernel"
 
 
+@pytest.mark.parametrize("shape", [(8, 8, 64), (32, 8, 128), (40, 2, 64)])
+@pytest.mark.parametrize("n_seqs", [1, 3, 9])
+@pytest.mark.parametrize("window", [None, 150])
+def test_tma_fed_decode_attention_with_key_splits(ops, shape, n_seqs, window):
+    """Few sequences: the keys of a (sequence, kv head) are split over a cluster of 16, 8 or 4 blocks, each with
+    a TMA ring of its own, and meet in the first block's shared memory. Sequences of one key, of fewer pages
+    than splits and of 40 pages; the same splits in the cp.async kernel give the same bits."""
+    heads, kv_heads, D = shape
+    dtype = torch.bfloat16
+    ref = TorchOps(dtype)
+    width = 40
+    rnd = random.Random(19 + n_seqs)
+    starts = [rnd.choice([0, 63, 64, 200, 1000, 2559]) for _ in range(n_seqs)]
+    starts[0] = 2559
+    slots = list(range(n_seqs))
+    rnd.shuffle(slots)
+    batch = make_batch(slots, starts, [1] * n_seqs)
+    qg = (1.5 + 0.1 * rand((D,), torch.float32, 81)).to(dtype)
+    kg = (1.5 + 0.1 * rand((D,), torch.float32, 82)).to(dtype)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    scale = 1.0 / math.sqrt(D)
+    results = []
+    before = ops.tma_decode_splits
+    for splits_by_tma in ({1, 2, 4, 8, 16}, set()):
+        cache = make_cache(n_seqs * width + 3, kv_heads, D, n_seqs, width, dtype, 80)
+        cache.window = window
+        qkv = rand((n_seqs, (heads + 2 * kv_heads) * D), dtype, 83)
+        ops.tma_decode_splits = splits_by_tma
+        try:
+            out = ops.rope_attention(qkv, heads, kv_heads, D, qg, kg, 1e-6, cos, sin, batch, cache, scale, window)
+        finally:
+            ops.tma_decode_splits = before
+        results.append((out, cache.k, cache.v))
+    ops.check()
+    for a, b, what in zip(results[0], results[1], ("output", "key pages", "value pages")):
+        assert torch.equal(a, b), f"{what} differ between the TMA-fed and the cp.async kernel"
+    ref_cache = make_cache(n_seqs * width + 3, kv_heads, D, n_seqs, width, dtype, 80)
+    ref_cache.window = window
+    want = ref.rope_attention(rand((n_seqs, (heads + 2 * kv_heads) * D), dtype, 83), heads, kv_heads, D, qg, kg, 1e-6, cos, sin,
+                              batch, ref_cache, scale, window)
+    close(results[0][0], want, dtype, f"TMA-fed decode attention with key splits {shape} seqs {n_seqs} window {window}")
+
+
 @pytest.mark.parametrize("shape", [(8, 8, 64), (32, 8, 128)])
 def test_tma_fed_decode_attention_round_a_wrapped_ring_of_pages(ops, shape):
     """A window of 150 keys in a ring of 6 pages, sequences thousands of tokens long: the positions' pages
