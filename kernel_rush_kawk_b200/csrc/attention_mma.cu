@@ -1140,6 +1140,12 @@ int launch_decode_tma(bf16* out, const bf16* qkv, int q_stride, int HQ, int HKV,
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
+  const float scale_log2 = scale * LOG2E;
+  if (splits == 1)  // no cluster: the plain launch, whose blocks the device places as it likes
+    return (int)launch_pdl(attention_decode_tma_kernel, dim3(1, HKV * row_tiles, n_seqs), dim3(TMA_THREADS), smem, stream,
+                           map_k, map_v, out, qkv, q_stride, HQ, HKV, q_gain, k_gain, gain_f32, cos_t, sin_t, eps, seq_slot,
+                           seq_start, table, width, k_cache, v_cache, scale_log2, window, row_tiles, n_pos, ring, inbox_rows,
+                           error);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, HKV * row_tiles, n_seqs);
   cfg.blockDim = dim3(TMA_THREADS);
@@ -1171,7 +1177,6 @@ int launch_decode_tma(bf16* out, const bf16* qkv, int q_stride, int HQ, int HKV,
     }
     if (!fits) return -8;
   }
-  const float scale_log2 = scale * LOG2E;
   return (int)cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel, map_k, map_v, out, qkv, q_stride, HQ, HKV, q_gain, k_gain,
                                  gain_f32, cos_t, sin_t, eps, seq_slot, seq_start, table, width, k_cache, v_cache, scale_log2,
                                  window, row_tiles, n_pos, ring, inbox_rows, error);
