@@ -470,8 +470,8 @@ struct HeadRow {
   static constexpr int PAIRS = (D / 2 + 31) / 32;
   float lo[PAIRS], hi[PAIRS], g_lo[PAIRS], g_hi[PAIRS], c[PAIRS], s[PAIRS];
 
-  // the row's values and gains: their addresses do not depend on the token's position
-  __device__ __forceinline__ void load_values(const bf16* __restrict__ src, const void* gain, int gain_f32, int lane) {
+  // the row's values: their addresses do not depend on the token's position
+  __device__ __forceinline__ void load_values(const bf16* __restrict__ src, int lane) {
     constexpr int HALF = D / 2;
 #pragma unroll
     for (int p = 0; p < PAIRS; ++p) {
@@ -479,6 +479,15 @@ struct HeadRow {
       const bool ok = i < HALF;
       lo[p] = ok ? __bfloat162float(src[i]) : 0.f;
       hi[p] = ok ? __bfloat162float(src[i + HALF]) : 0.f;
+    }
+  }
+  // the norm's gains: weights, which no kernel writes
+  __device__ __forceinline__ void load_gains(const void* gain, int gain_f32, int lane) {
+    constexpr int HALF = D / 2;
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int i = lane + 32 * p;
+      const bool ok = i < HALF;
       g_lo[p] = (ok && gain) ? load_gain<bf16>(gain, i, gain_f32) : 1.f;
       g_hi[p] = (ok && gain) ? load_gain<bf16>(gain, i + HALF, gain_f32) : 1.f;
     }
@@ -537,10 +546,11 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);                       // page buffers, later the partials
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw + fused_base_bytes(FSTAGES));  // [16][DP] rotated queries
   bf16* kv_new = q_s + 16 * DP;                                         // [2][D] the new token's key and value
-  float* inbox = reinterpret_cast<float*>(kv_new + 2 * D);              // [splits][inbox_rows][D + 2], used in block 0
+  float* inbox = reinterpret_cast<float*>(kv_new + 2 * D);              // [splits][inbox_rows][D / splits + 2, padded to a multiple of 4]
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   KRK_TRACE_DECL
+  KRK_TRACE_MARKS
   // "I have started": waited for only before the first write into another block's shared memory
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   grid_launch_dependents();
@@ -578,16 +588,14 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     cp_async_commit();
   };
 #pragma unroll
-  for (int i = 0; i < FSTAGES - 1; ++i) issue(j_lo + i);
-  grid_dependency_wait();
-  KRK_TRACE_READY
-
+  for (int i = 0; i < FSTAGES; ++i) issue(j_lo + i);  // every stage: with few pages per block all of them travel now
   // The new token's rows. Warp w takes query rows w, w + 4, ... of this tile (rows beyond G
   // are zero); the key and value rows go to the warp with the fewest query rows, in every
-  // block (only the block whose keys include the new token uses them). All loads whose
-  // addresses do not need the position are issued before the position is first used, and
-  // all loads of a row before any arithmetic: the prologue costs about two memory
-  // latencies, whatever the number of rows.
+  // block (only the block whose keys include the new token uses them). The gains and the
+  // position's table rows are weights, which no kernel writes: they are requested before
+  // the wait on the kernel that writes the rows, and all loads of a row are issued before
+  // any arithmetic, so that after the wait the prologue costs one memory latency,
+  // whatever the number of rows.
   const bf16* row = qkv + (size_t)seq * q_stride;
   const int q_rows = min(16, G - rt * 16);
   const int k_warp = q_rows % 4;
@@ -595,26 +603,34 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   HeadRow regs[MAX_ROWS];
   HeadRow k_regs;
   float v_regs[(D + 31) / 32];
+  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
+  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i)
+    if (warp + 4 * i < q_rows) {
+      regs[i].load_gains(q_gain, gain_f32, lane);
+      regs[i].load_angles(cos_row, sin_row, lane);
+    }
+  if (warp == k_warp) {
+    k_regs.load_gains(k_gain, gain_f32, lane);
+    k_regs.load_angles(cos_row, sin_row, lane);
+  }
+  KRK_TRACE_MARK(0)
+  grid_dependency_wait();
+  KRK_TRACE_READY
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i) {
     const int r = warp + 4 * i;
-    if (r < q_rows) regs[i].load_values(row + (size_t)(kh * G + rt * 16 + r) * D, q_gain, gain_f32, lane);
+    if (r < q_rows) regs[i].load_values(row + (size_t)(kh * G + rt * 16 + r) * D, lane);
   }
   if (warp == k_warp) {
-    k_regs.load_values(row + (size_t)(HQ + kh) * D, k_gain, gain_f32, lane);
+    k_regs.load_values(row + (size_t)(HQ + kh) * D, lane);
 #pragma unroll
     for (int i = 0; i < (D + 31) / 32; ++i) {
       const int d = lane + 32 * i;
       v_regs[i] = d < D ? __bfloat162float(row[(size_t)(HQ + HKV + kh) * D + d]) : 0.f;
     }
   }
-
-  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
-  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
-#pragma unroll
-  for (int i = 0; i < MAX_ROWS; ++i)
-    if (warp + 4 * i < q_rows) regs[i].load_angles(cos_row, sin_row, lane);
-  if (warp == k_warp) k_regs.load_angles(cos_row, sin_row, lane);
 
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i) {
@@ -625,6 +641,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
       for (int d = lane; d < D; d += 32) q_s[r * DP + d] = __float2bfloat16_rn(0.f);
     }
   }
+  KRK_TRACE_MARK(1)
   if (owns_new && warp == k_warp) {
     k_regs.finish(kv_new, k_gain != nullptr, cos_t != nullptr, eps, lane);
 #pragma unroll
@@ -660,7 +677,6 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
 
   for (int j = j_lo; j <= j_hi; ++j) {
     const int stage = (j - j_lo) % FSTAGES;
-    issue(j + FSTAGES - 1);            // into the stage that the previous iteration finished with
     cp_async_wait<FSTAGES - 1>();      // all but the newest FSTAGES - 1 groups: page j has landed
     __syncthreads();
     bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
@@ -685,16 +701,20 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     softmax_update<2>(s, m, l, o);
     pv_tile<2>(o, s, vs, key0, lane);
     __syncthreads();
+    issue(j + FSTAGES);                // into the stage that this iteration has finished with
   }
 
+  KRK_TRACE_MARK(2)
   cp_async_wait<0>();
-  // Merge the four warps through shared memory, in warp order, and push the block's partial
-  // (m, l, o[D]) per row straight into block 0's inbox through distributed shared memory.
-  // One cluster barrier later block 0 holds every split's partial locally and merges them in
-  // split order; the other blocks are done.
+  // Merge the four warps through shared memory, in warp order; then every block of the cluster
+  // takes D / splits of the head's dimensions: a block pushes that slice of its partial
+  // o[D] per row, with the row's (m, l), into the inbox of the block that owns the slice,
+  // through distributed shared memory. One cluster barrier later each block holds every
+  // split's partial of its slice and merges them in split order, so the merge and the
+  // store of the result are spread over the cluster and an inbox is a few kilobytes.
   constexpr int RP = D + 2;
   float* red = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][RP]; the page buffers are free now
-  float* inbox0 = cluster.map_shared_rank(inbox, 0);  // [splits][inbox_rows][RP] in block 0
+  const int DS = D / n_splits, IW = (DS + 2 + 3) & ~3;  // an inbox row: DS values, m, l, padded to 16 bytes
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float* dst = red + ((size_t)warp * 16 + g + 8 * h) * RP;
@@ -706,6 +726,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     }
   }
   __syncthreads();
+  KRK_TRACE_MARK(3)
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block of the cluster has started
   for (int r = warp; r < q_rows; r += 4) {
     float mw[4], big = -INFINITY;
@@ -715,46 +736,56 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     float wgt[4], lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
-    float* dst = inbox0 + ((size_t)split * inbox_rows + r) * RP;
-    for (int d = lane; d < D; d += 32) {
-      float acc = 0.f;
+    const size_t at = ((size_t)split * inbox_rows + r) * IW;
+    if (DS % 4 == 0) {  // four neighbouring dimensions have one owner: one 16-byte store through the cluster's network
+      for (int d = 4 * lane; d < D; d += 128) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
-      dst[d] = acc;
+        for (int w = 0; w < 4; ++w) {
+          const float2* src = reinterpret_cast<const float2*>(red + ((size_t)w * 16 + r) * RP + d);
+          const float2 a = src[0], b = src[1];
+          acc.x += wgt[w] * a.x;
+          acc.y += wgt[w] * a.y;
+          acc.z += wgt[w] * b.x;
+          acc.w += wgt[w] * b.y;
+        }
+        *reinterpret_cast<float4*>(cluster.map_shared_rank(inbox, d / DS) + at + d % DS) = acc;
+      }
+    } else {
+      for (int d = lane; d < D; d += 32) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+        cluster.map_shared_rank(inbox, d / DS)[at + d % DS] = acc;
+      }
     }
-    if (lane == 0) { dst[D] = big; dst[D + 1] = lsum; }
+    if (lane < n_splits) {
+      float* dst = cluster.map_shared_rank(inbox, lane) + at;
+      dst[DS] = big;
+      dst[DS + 1] = lsum;
+    }
   }
   KRK_TRACE_READY
-  cluster.sync();  // every block's partial has arrived in block 0
-  if (split == 0) {
-    for (int r = warp; r < q_rows; r += 4) {
-      const float* mine = inbox + (size_t)r * RP;
-      const size_t step = (size_t)inbox_rows * RP;
-      float big = -INFINITY;
-      for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, mine[s2 * step + D]);
-      float lsum = 0.f;
-      float acc[(D + 31) / 32];
-#pragma unroll
-      for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
-      for (int s2 = 0; s2 < n_splits; ++s2) {
-        const float w = exp2f(mine[s2 * step + D] - big);
-        lsum += w * mine[s2 * step + D + 1];
-#pragma unroll
-        for (int i = 0; i < (D + 31) / 32; ++i) {
-          const int d = lane + 32 * i;
-          if (d < D) acc[i] += w * mine[s2 * step + d];
-        }
-      }
-      const float inv = 1.0f / lsum;
-      bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
-#pragma unroll
-      for (int i = 0; i < (D + 31) / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
-      }
+  KRK_TRACE_MARK(4)
+  cluster.sync();  // every block's slice of every partial has arrived
+  KRK_TRACE_MARK(5)
+  for (int idx = threadIdx.x; idx < q_rows * DS; idx += THREADS) {
+    const int r = idx / DS, d = idx % DS;
+    const float* mine = inbox + (size_t)r * IW;
+    const size_t step = (size_t)inbox_rows * IW;
+    float big = -INFINITY;
+    for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, mine[s2 * step + DS]);
+    float lsum = 0.f, acc = 0.f;
+    for (int s2 = 0; s2 < n_splits; ++s2) {
+      const float w = exp2f(mine[s2 * step + DS] - big);
+      lsum += w * mine[s2 * step + DS + 1];
+      acc += w * mine[s2 * step + d];
     }
+    const float inv = 1.0f / lsum;
+    out[((size_t)seq * HQ + kh * G + rt * 16 + r) * D + split * DS + d] = __float2bfloat16_rn(acc * inv);
   }
   KRK_TRACE_END(2)
+  KRK_TRACE_MARKS_OUT(3)
 }
 
 template <int FSTAGES>
@@ -766,8 +797,8 @@ int launch_decode_fused(bf16* out, const bf16* qkv, int q_stride, int HQ, int HK
   const int row_tiles = (G + 15) / 16;
   const int inbox_rows = G < 16 ? G : 16;
   const size_t smem = fused_base_bytes(FSTAGES) + (size_t)(16 * DP + 2 * D) * sizeof(bf16) +
-                      (size_t)splits * inbox_rows * (D + 2) * sizeof(float);
-  if (smem > 220 * 1024) return -2;
+                      (size_t)splits * inbox_rows * ((D / splits + 2 + 3) & ~3) * sizeof(float);
+  if (smem > 220 * 1024 || D % splits) return -2;
   auto kern = attention_decode_fused_kernel<FSTAGES>;
   static size_t configured = 0;
   if (smem > configured) {
@@ -914,7 +945,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
 
   // ---- consumers: warps 0..3 ----
-  grid_dependency_wait();
+  // gains and the position's table rows are weights: requested before the wait on the kernel that writes the rows
   const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
   const size_t head_off = (size_t)kh * KRK_PAGE * D;
   const bf16* row = qkv + (size_t)seq * q_stride;
@@ -924,25 +955,32 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   HeadRow regs[MAX_ROWS];
   HeadRow k_regs;
   float v_regs[(D + 31) / 32];
+  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
+  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
+#pragma unroll
+  for (int i = 0; i < MAX_ROWS; ++i)
+    if (warp + 4 * i < q_rows) {
+      regs[i].load_gains(q_gain, gain_f32, lane);
+      regs[i].load_angles(cos_row, sin_row, lane);
+    }
+  if (warp == k_warp) {
+    k_regs.load_gains(k_gain, gain_f32, lane);
+    k_regs.load_angles(cos_row, sin_row, lane);
+  }
+  grid_dependency_wait();
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i) {
     const int r = warp + 4 * i;
-    if (r < q_rows) regs[i].load_values(row + (size_t)(kh * G + rt * 16 + r) * D, q_gain, gain_f32, lane);
+    if (r < q_rows) regs[i].load_values(row + (size_t)(kh * G + rt * 16 + r) * D, lane);
   }
   if (warp == k_warp) {
-    k_regs.load_values(row + (size_t)(HQ + kh) * D, k_gain, gain_f32, lane);
+    k_regs.load_values(row + (size_t)(HQ + kh) * D, lane);
 #pragma unroll
     for (int i = 0; i < (D + 31) / 32; ++i) {
       const int d = lane + 32 * i;
       v_regs[i] = d < D ? __bfloat162float(row[(size_t)(HQ + HKV + kh) * D + d]) : 0.f;
     }
   }
-  const bf16* cos_row = cos_t ? cos_t + (size_t)pos * (D / 2) : nullptr;
-  const bf16* sin_row = sin_t ? sin_t + (size_t)pos * (D / 2) : nullptr;
-#pragma unroll
-  for (int i = 0; i < MAX_ROWS; ++i)
-    if (warp + 4 * i < q_rows) regs[i].load_angles(cos_row, sin_row, lane);
-  if (warp == k_warp) k_regs.load_angles(cos_row, sin_row, lane);
 #pragma unroll
   for (int i = 0; i < MAX_ROWS; ++i) {
     const int r = warp + 4 * i;

@@ -63,9 +63,9 @@ def build_dir() -> Path:
     for d in cands:
         try:
             d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".probe_{os.getpid()}"
-            probe.write_text("ok")
-            probe.unlink()
+            fd, probe = tempfile.mkstemp(prefix=".probe_", dir=d)  # a name of its own: threads and processes probe at once
+            os.close(fd)
+            os.unlink(probe)
             return d
         except OSError:
             continue

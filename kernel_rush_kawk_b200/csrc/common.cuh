@@ -54,16 +54,34 @@ __device__ __forceinline__ unsigned long long krk_now() {
   if (threadIdx.x == 0) {                                                    \
     unsigned int i__ = atomicAdd(&krk_trace_count, 1u);                      \
     if (i__ < KRK_TRACE_CAP) {                                               \
-      krk_trace_buf[4 * i__] = ((unsigned long long)(kind) << 32) | blockIdx.x; \
+      krk_trace_buf[4 * i__] = ((unsigned long long)(kind) << 32) | blockIdx.x | (blockIdx.y << 16); \
       krk_trace_buf[4 * i__ + 1] = t_begin__;                                \
       krk_trace_buf[4 * i__ + 2] = t_ready__;                                \
       krk_trace_buf[4 * i__ + 3] = krk_now();                                \
     }                                                                        \
   }
+#define KRK_TRACE_MARKS unsigned long long mark__[6] = {0, 0, 0, 0, 0, 0};
+#define KRK_TRACE_MARK(i) mark__[i] = krk_now();
+#define KRK_TRACE_REC(kind, a, b, c)                                         \
+  if (threadIdx.x == 0) {                                                    \
+    unsigned int i__ = atomicAdd(&krk_trace_count, 1u);                      \
+    if (i__ < KRK_TRACE_CAP) {                                               \
+      krk_trace_buf[4 * i__] = ((unsigned long long)(kind) << 32) | blockIdx.x | (blockIdx.y << 16); \
+      krk_trace_buf[4 * i__ + 1] = (a);                                      \
+      krk_trace_buf[4 * i__ + 2] = (b);                                      \
+      krk_trace_buf[4 * i__ + 3] = (c);                                      \
+    }                                                                        \
+  }
+#define KRK_TRACE_MARKS_OUT(kind)                                            \
+  KRK_TRACE_REC(kind, mark__[0], mark__[1], mark__[2])                       \
+  KRK_TRACE_REC((kind) + 1, mark__[3], mark__[4], mark__[5])
 #else
 #define KRK_TRACE_DECL
 #define KRK_TRACE_READY
 #define KRK_TRACE_END(kind)
+#define KRK_TRACE_MARKS
+#define KRK_TRACE_MARK(i)
+#define KRK_TRACE_MARKS_OUT(kind)
 #endif
 
 template <typename... KArgs, typename... Args>

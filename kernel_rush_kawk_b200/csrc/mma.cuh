@@ -23,6 +23,21 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr(smem)), "l"(gmem));
 }
+// The same copy for bytes that are read once per step (weights): marked to leave L2 first, so that what every
+// layer reads again (positions, page tables, rotation tables, gains, the rows in flight) stays there.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void cp_async_16_stream(void* smem, const void* gmem, uint64_t policy) {
+#ifdef KRK_NO_L2_HINT
+  (void)policy;
+  cp_async_16(smem, gmem);
+#else
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem)), "l"(gmem), "l"(policy));
+#endif
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 

@@ -108,14 +108,15 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
     xsrc[j] = x + (size_t)min(m, M - 1) * K + 8 * t;
   }
 
+  const uint64_t stream_policy = l2_evict_first_policy();
   auto issue_w = [&](int i) {  // weights of chunk i of this warp's slice into stage i % STAGES
     if (i < nc) {
       uint4* dst = ring + ((size_t)(i % STAGES) * SLOTS) * THREADS + threadIdx.x;
       const size_t off = (size_t)(c_begin + i) * CHUNK;
 #pragma unroll
       for (int s = 0; s < TILES; ++s) {
-        cp_async_16(dst + (s * 2 + 0) * THREADS, wrow[s][0] + off);
-        cp_async_16(dst + (s * 2 + 1) * THREADS, wrow[s][1] + off);
+        cp_async_16_stream(dst + (s * 2 + 0) * THREADS, wrow[s][0] + off, stream_policy);
+        cp_async_16_stream(dst + (s * 2 + 1) * THREADS, wrow[s][1] + off, stream_policy);
       }
     }
   };
@@ -367,10 +368,13 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
            int N, int K, float eps, cudaStream_t stream) {
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
   // Between two and three blocks per SM: small blocks, but with rings as deep as three of them fit beside one
-  // another, since what bounds a block is the bytes it has in flight.
+  // another, since what bounds a block is the bytes it has in flight. With the norm prologue (one or two rows:
+  // the QKV projection of a step of one sequence) the ring is shallower, so that the blocks of the kernel that
+  // follows, the single-token attention with its 70 KB of pages, fit beside three of these and request their
+  // pages while this kernel still streams (one sequence of the 4B shape: 1.98 -> 1.95 ms a step).
   if constexpr (!SWIGLU && RT == 1) {
     if (blocks > 2 * 148 && blocks <= 3 * 148)
-      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 14 : NT == 1 ? 11 : 8)>(
+      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 10 : NT == 1 ? 11 : 8)>(
           out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
   }
   if (blocks > 2 * 148 && blocks <= 5 * 148)
