@@ -589,6 +589,8 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   };
 #pragma unroll
   for (int i = 0; i < FSTAGES; ++i) issue(j_lo + i);  // every stage: with few pages per block all of them travel now
+  // the page that takes the new token's key and value (read here, ahead of the wait, by the block that writes them)
+  const int page_new = (owns_new && rt == 0) ? table[(size_t)slot * width + j_last % width] : 0;
   // The new token's rows. Warp w takes query rows w, w + 4, ... of this tile (rows beyond G
   // are zero); the key and value rows go to the warp with the fewest query rows, in every
   // block (only the block whose keys include the new token uses them). The gains and the
@@ -651,8 +653,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     }
     __syncwarp();
     if (rt == 0) {
-      const int page = table[(size_t)slot * width + j_last % width];
-      const size_t at = (size_t)page * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
+      const size_t at = (size_t)page_new * page_stride + head_off + (size_t)(pos % KRK_PAGE) * D;
       for (int d = lane; d < D; d += 32) {
         k_cache[at + d] = kv_new[d];
         v_cache[at + d] = kv_new[D + d];

@@ -42,7 +42,7 @@ _SIGNATURES = {
     "krk_gather_rows": [_P, _P, _P, c_int, c_int, c_int, _P, c_int, _P],
     "krk_swiglu": [_P, _P, c_int, c_int, c_int, _P],
     "krk_qk_norm_rope_write": [_P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int,
-                               c_float, c_int, _P, c_int, _P],
+                               c_int, c_float, c_int, _P, c_int, _P],
     "krk_gemm_nt": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_select_tokens": [_P, _P, c_int, c_int, c_float, c_uint, _P, c_uint, _P, _P, _P, _P, _P],
     "krk_gemm_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
@@ -316,12 +316,23 @@ class Kernels:
     def qk_norm_rope_write(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache):
         gain = q_gain if q_gain is not None else k_gain
         n_pos = cos.shape[0] if cos is not None else 0x7fffffff
+        rot = self._rotated_width(cos, head_dim)
         self._ok(self.core.krk_qk_norm_rope_write(
             qkv.data_ptr(), _ptr(q_gain), _ptr(k_gain), int(gain is not None and gain.dtype == torch.float32),
             _ptr(cos), _ptr(sin), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(),
             cache.table.data_ptr(), cache.width, cache.k.data_ptr() if kv_in_row else None,
-            cache.v.data_ptr() if kv_in_row else None, qkv.shape[0], heads, kv_in_row, head_dim, eps, n_pos,
+            cache.v.data_ptr() if kv_in_row else None, qkv.shape[0], heads, kv_in_row, head_dim, rot, eps, n_pos,
             self.error.data_ptr(), _code(qkv.dtype), self._stream()), "q/k norm + rope + cache write")
+
+    @staticmethod
+    def _rotated_width(cos, head_dim: int) -> int:
+        """The width of the head that the tables rotate: all of it, or its first 2 * columns elements."""
+        if cos is None:
+            return head_dim
+        rot = 2 * cos.shape[1]
+        if rot > head_dim or not cos.is_contiguous():
+            raise KernelError(f"rotary tables of {cos.shape[1]} columns do not fit a head of {head_dim} (at most half of it, contiguous)")
+        return rot
 
     def rope_attention(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache, scale,
                        window):
@@ -329,7 +340,8 @@ class Kernels:
         bfloat16 runs them as one kernel; everything else as two."""
         lib = self._attn_lib(head_dim)
         if (batch.is_decode and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and kv_in_row > 0
-                and hasattr(lib, "krk_attention_decode_fused") and qkv.shape[0] > 0):
+                and hasattr(lib, "krk_attention_decode_fused") and qkv.shape[0] > 0
+                and self._rotated_width(cos, head_dim) == head_dim):  # the fused kernel rotates the whole head
             n = batch.n_seqs
             out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
             row_tiles = -(-(heads // cache.kv_heads) // 16)

@@ -9,6 +9,9 @@
 // cache page of the row's position, v heads are copied there raw (rope.py:139-144).
 // HKV may be 0: a run that reads another run's cache has queries only.
 // One warp per (row, head); the head size is a run-time argument (even, <= 512).
+// A rotation of part of the head (rot < D, the tables then [positions, rot/2]) pairs element i
+// with element i + rot/2 for i < rot/2 and leaves elements rot..D-1 as the norm made them; the
+// norm is over the whole head. The general kernel serves it; the 16-byte-lane kernels rotate the whole head.
 #include "common.cuh"
 
 namespace {
@@ -19,7 +22,7 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const void* __res
                                           const T* __restrict__ sin_t, const int* __restrict__ row_seq,
                                           const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
                                           const int* __restrict__ table, int width, T* __restrict__ k_cache,
-                                          T* __restrict__ v_cache, int rows, int HQ, int HKV, int D, float eps,
+                                          T* __restrict__ v_cache, int rows, int HQ, int HKV, int D, int rot, float eps,
                                           int n_pos, int* error) {
   grid_launch_dependents();
   grid_dependency_wait();
@@ -49,6 +52,35 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const void* __res
   const void* gain = head < HQ ? q_gain : k_gain;
   if (pos < 0 || pos >= n_pos) {
     if (lane == 0 && error) atomicExch(error, 2);
+    return;
+  }
+  if (rot < D) {  // part of the head is rotated: pairs (i, i + rot/2) below rot, the rest only normalised
+    const int rh = rot / 2;
+    float sq = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float a = to_float<T>(src[i]);
+      sq += a * a;
+    }
+    sq = warp_sum(sq);
+    const float r = gain ? rsqrtf(sq / (float)D + eps) : 1.f;
+    auto normed = [&](int i) {
+      const float y = to_float<T>(src[i]);
+      return gain ? round_to<T>(load_gain<T>(gain, i, gain_f32) * round_to<T>(y * r)) : y;
+    };
+    for (int i = lane; i < rh; i += 32) {  // both elements of a pair are read before either is written (q in place)
+      float y1 = normed(i), y2 = normed(i + rh);
+      if (cos_t) {
+        const float c = to_float<T>(cos_t[(size_t)pos * rh + i]);
+        const float s = to_float<T>(sin_t[(size_t)pos * rh + i]);
+        const float o1 = round_to<T>(y1 * c) + round_to<T>(-y2 * s);
+        const float o2 = round_to<T>(y2 * c) + round_to<T>(y1 * s);
+        y1 = o1;
+        y2 = o2;
+      }
+      dst[i] = from_float<T>(y1);
+      dst[i + rh] = from_float<T>(y2);
+    }
+    for (int i = rot + lane; i < D; i += 32) dst[i] = from_float<T>(normed(i));
     return;
   }
   // each lane owns the pairs (i, i + half), i = lane, lane + 32, ...
@@ -253,16 +285,18 @@ qk_norm_rope_write_row_kernel(bf16* __restrict__ qkv, const void* __restrict__ q
 constexpr int ROW_KERNEL_MIN_ROWS = 256;
 
 // gains may be null (no q/k norm); cos/sin may be null (no rotation); the cache
-// pointers are unused when HKV == 0.
+// pointers are unused when HKV == 0. rot: the rotated width (even, <= D; the tables are [positions, rot/2]).
 KRK_API int krk_qk_norm_rope_write(void* qkv, const void* q_gain, const void* k_gain, int gain_f32, const void* cos_t,
                                    const void* sin_t, const int* row_seq, const int* row_pos, const int* seq_slot,
                                    const int* table, int width, void* k_cache, void* v_cache, int rows, int HQ, int HKV,
-                                   int D, float eps, int n_pos, int* error, int dtype, cudaStream_t stream) {
+                                   int D, int rot, float eps, int n_pos, int* error, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (D % 2 || D > 4096) return -2;
+  if (!cos_t) rot = D;
+  if (rot % 2 || rot <= 0 || rot > D) return -2;
   const long long items = (long long)rows * (HQ + 2 * HKV);
   const bool gains_aligned = gain_f32 || ((((uintptr_t)q_gain) | ((uintptr_t)k_gain)) & 15) == 0;  // 16-byte gain loads
-  if (dtype == KRK_DTYPE_BF16 && gains_aligned && (D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) {
+  if (dtype == KRK_DTYPE_BF16 && gains_aligned && rot == D && (D == 16 || D == 32 || D == 64 || D == 128 || D == 256)) {
     if (rows >= ROW_KERNEL_MIN_ROWS)
       return (int)launch_pdl(qk_norm_rope_write_row_kernel, dim3((unsigned)rows), dim3(256), 0, stream, (bf16*)qkv, q_gain,
                              k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, row_seq, row_pos, seq_slot, table,
@@ -281,8 +315,8 @@ KRK_API int krk_qk_norm_rope_write(void* qkv, const void* q_gain, const void* k_
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(qk_norm_rope_write_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
         (float*)qkv, q_gain, k_gain, gain_f32, (const float*)cos_t, (const float*)sin_t, row_seq, row_pos, seq_slot,
-        table, width, (float*)k_cache, (float*)v_cache, rows, HQ, HKV, D, eps, n_pos, error);
+        table, width, (float*)k_cache, (float*)v_cache, rows, HQ, HKV, D, rot, eps, n_pos, error);
   return (int)launch_pdl(qk_norm_rope_write_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
         (bf16*)qkv, q_gain, k_gain, gain_f32, (const bf16*)cos_t, (const bf16*)sin_t, row_seq, row_pos, seq_slot, table,
-        width, (bf16*)k_cache, (bf16*)v_cache, rows, HQ, HKV, D, eps, n_pos, error);
+        width, (bf16*)k_cache, (bf16*)v_cache, rows, HQ, HKV, D, rot, eps, n_pos, error);
 }

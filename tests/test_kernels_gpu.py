@@ -324,6 +324,46 @@ def test_rope_write_many_rows(ops, dtype, shape):
     assert torch.equal(qkv[:, heads * D:], qkv_ref[:, heads * D:]), "the step's own k and v columns stay as they were"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(3, 1, 16, 8), (6, 2, 48, 20), (8, 2, 128, 64), (5, 1, 80, 2)])
+@pytest.mark.parametrize("gains", [True, False])
+def test_rope_write_rotates_part_of_the_head(ops, dtype, shape, gains):
+    """Tables narrower than half the head: the first rot elements are rotated in pairs (i, i + rot/2), the
+    others only normalised (over the whole head); few rows and many; then a single-token step, which must
+    not take the kernel that rotates whole heads."""
+    heads, kv_heads, D, rot = shape
+    ref = TorchOps(dtype)
+    width, n_slots = 8, 4
+    cache = make_cache(40, kv_heads, D, n_slots, width, dtype, 41)
+    ref_cache = SimpleNamespace(**vars(cache))
+    ref_cache.k, ref_cache.v = cache.k.clone(), cache.v.clone()
+    inv = 1.0 / (1e4 ** (torch.arange(0, rot, 2, device="cuda").float() / rot))
+    ang = torch.arange(width * PAGE, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dtype).contiguous(), ang.sin().to(dtype).contiguous()
+    qg = (1.5 + 0.1 * rand((D,), torch.float32, 42)).to(dtype) if gains else None
+    kg = (0.7 + 0.1 * rand((D,), torch.float32, 43)).to(dtype) if gains else None
+    scale = 1.0 / math.sqrt(D)
+    for s, (slots, starts, q_lens) in enumerate([([1, 3, 0], [0, 0, 0], [300, 7, 41]), ([3, 1], [7, 300], [5, 1]),
+                                                 ([0, 1, 3], [41, 301, 12], [1, 1, 1])]):
+        batch = make_batch(slots, starts, q_lens)
+        qkv = rand((batch.n_rows, (heads + 2 * kv_heads) * D), dtype, 44 + s, 1.0)
+        qkv_ref = qkv.clone()
+        if s < 2:
+            ops.qk_norm_rope_write(qkv, heads, kv_heads, D, qg, kg, 1e-5, cos, sin, batch, cache)
+            ref.qk_norm_rope_write(qkv_ref, heads, kv_heads, D, qg, kg, 1e-5, cos, sin, batch, ref_cache)
+            close(qkv[:, :heads * D], qkv_ref[:, :heads * D], dtype, f"rotated queries, step {s}")
+            if not gains:
+                got_q = qkv[:, :heads * D].view(-1, heads, D)
+                assert torch.equal(got_q[..., rot:], qkv_ref[:, :heads * D].view(-1, heads, D)[..., rot:]), "beyond rot: untouched"
+        else:
+            got = ops.rope_attention(qkv, heads, kv_heads, D, qg, kg, 1e-5, cos, sin, batch, cache, scale, None)
+            want = ref.rope_attention(qkv_ref, heads, kv_heads, D, qg, kg, 1e-5, cos, sin, batch, ref_cache, scale, None)
+            close(got, want, dtype, "single-token step with a partial rotation")
+        close(cache.k, ref_cache.k, dtype, f"key pages, step {s}")
+        assert torch.equal(cache.v, ref_cache.v), "values are copied raw"
+        ref_cache.k.copy_(cache.k)
+
+
 @pytest.mark.parametrize("rows", [3, 300])
 def test_a_position_outside_the_rotary_table_is_flagged(ops, rows):
     """A row whose position lies beyond the tables is reported through the error word and stores

@@ -114,6 +114,58 @@ def test_attention_part_alone(dtype, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_part_with_a_rotation_of_part_of_the_head(dtype):
+    """Another position encoding for the same mixer: tables that cover the first 24 of a head's 48 elements.
+    The attention part takes them as they are (the rotated width is the tables' own); whole, in two pieces,
+    and with the last tokens one by one, against a plain whole-sequence computation written out here."""
+    from kernel_rush_kawk_b200.cache import SequenceCache
+    from kernel_rush_kawk_b200.parts import GQAttention, RotaryTable
+
+    rt = runtime(dtype)
+    rounding = None if dtype == torch.float32 else torch.bfloat16
+    rnd = (lambda x: x) if rounding is None else (lambda x: x.to(rounding).float())
+    H, HQ, HKV, D, ROT, T, EPS = 80, 4, 2, 48, 24, 75, 1e-5
+    part = GQAttention({"hidden": H, "heads": HQ, "kv_heads": HKV, "head_dim": D, "eps": EPS})
+    rope = RotaryTable({"theta": 1e4, "dim": ROT, "positions": 128})
+    rope.bind({}, rt)
+    part.set_position(rope)
+    w = {"q_proj": rand((HQ * D, H), 1, 0.1), "k_proj": rand((HKV * D, H), 2, 0.1), "v_proj": rand((HKV * D, H), 3, 0.1),
+         "o_proj": rand((H, HQ * D), 4, 0.1), "q_norm": 1.5 + 0.1 * rand((D,), 5), "k_norm": 0.8 + 0.1 * rand((D,), 6)}
+    w = {k: v.to(dtype) for k, v in w.items()}
+    part.bind({k: v.cuda() for k, v in w.items()}, rt)
+    h = rand((T, H), 7).to(dtype)
+
+    # the plain computation: per-head norm over all 48 elements, pairs (i, i + 12) of the first 24 rotated
+    pc, ps = plain.rope_tables(ROT, 1e4, T, torch.float32, rounding)
+    f = {k: v.float() for k, v in w.items()}
+
+    def norm_rotate(x, gain):
+        r = torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + EPS)
+        y = rnd(gain * rnd(x * r))
+        y1, y2, rest = y[..., :ROT // 2], y[..., ROT // 2:ROT], y[..., ROT:]
+        c, s_ = pc[:, None, :], ps[:, None, :]
+        return torch.cat([rnd(rnd(y1 * c) + rnd(-y2 * s_)), rnd(rnd(y2 * c) + rnd(y1 * s_)), rest], dim=-1)
+
+    q = norm_rotate(plain.linear(h.float(), f["q_proj"], rounding).view(T, HQ, D), f["q_norm"])
+    k = norm_rotate(plain.linear(h.float(), f["k_proj"], rounding).view(T, HKV, D), f["k_norm"])
+    v = plain.linear(h.float(), f["v_proj"], rounding).view(T, HKV, D)
+    want = plain.linear(plain.causal_gqa_attention(q, k, v, None, rounding), f["o_proj"], rounding)
+
+    for pieces in ([T], [40, 35], [70, 1, 1, 1, 1, 1]):
+        cache = SequenceCache([part.cache_need()], 128, 2, 128, rt.device, dtype, step_tokens=64)
+        slot = cache.alloc()
+        got, start = [], 0
+        for n in pieces:
+            cache.reserve(slot, start + n)
+            cache.sync()
+            ctx = context(rt, [slot], [start], [n], cache)
+            got.append(part.forward(ctx, h[start:start + n].cuda(), cache.view(0)))
+            cache.advance(slot, n)
+            start += n
+        assert_close(torch.cat(got), want, NAME[dtype], f"attention part with a partial rotation, pieces {pieces}", kernel=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu_part_and_block_alone(dtype):
     from kernel_rush_kawk_b200.cache import SequenceCache
     from kernel_rush_kawk_b200.parts import GQAttention, PreNormBlock, RMSNorm, RotaryTable, Stream, SwiGLU

@@ -76,7 +76,8 @@ class TorchOps:
 
     # -- attention ----------------------------------------------------------
     def qk_norm_rope_write(self, qkv, heads, kv_in_row, head_dim, q_gain, k_gain, eps, cos, sin, batch, cache):
-        D, half = head_dim, head_dim // 2
+        D = head_dim
+        half = cos.shape[1] if cos is not None else D // 2  # the rotated width is twice the tables' columns
         rows = qkv.shape[0]
         pos = batch.row_pos.long()
         view = qkv.view(rows, heads + 2 * kv_in_row, D)
@@ -88,9 +89,9 @@ class TorchOps:
                 x = self.rt(gain.float() * self.rt(x * r))
             if cos is not None:
                 c, s = cos[pos].float()[:, None, :], sin[pos].float()[:, None, :]
-                x1, x2 = x[..., :half], x[..., half:]
+                x1, x2, rest = x[..., :half], x[..., half:2 * half], x[..., 2 * half:]
                 x = torch.cat([self.rt(self.rt(x1 * c) + self.rt(-x2 * s)),
-                               self.rt(self.rt(x2 * c) + self.rt(x1 * s))], dim=-1)
+                               self.rt(self.rt(x2 * c) + self.rt(x1 * s)), rest], dim=-1)
             return x.to(self.dtype)
 
         view[:, :heads] = norm_rope(view[:, :heads], q_gain)
