@@ -371,17 +371,13 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
   // another, since what bounds a block is the bytes it has in flight. With the norm prologue (one or two rows:
   // the QKV projection of a step of one sequence) the ring is shallower, so that the blocks of the kernel that
   // follows, the single-token attention with its 70 KB of pages, fit beside three of these and request their
-  // pages while this kernel still streams (one sequence of the 4B shape: 1.98 -> 1.95 ms a step). The same holds
-  // without the prologue: eight loads where eleven just fitted three blocks an SM made a step of eight sequences
-  // 2.17 -> 2.14 ms.
+  // pages while this kernel still streams (one sequence of the 4B shape: 1.98 -> 1.95 ms a step, together with
+  // the L2 hint of the weight copies). Without the prologue (three to sixteen rows) the depth makes no
+  // difference inside a step: eight loads against eleven at eight rows, six against eight at sixteen, each
+  // within 0.3 % in alternating runs.
   if constexpr (!SWIGLU && RT == 1) {
-    if constexpr (!NORM && NT == 2) {  // EXPERIMENT
-      static const bool shallow = getenv("KRK_QKV_RING6") != nullptr;
-      if (shallow && blocks > 2 * 148 && blocks <= 3 * 148)
-        return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, 6>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
-    }
     if (blocks > 2 * 148 && blocks <= 3 * 148)
-      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 10 : 8)>(
+      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 10 : NT == 1 ? 11 : 8)>(
           out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
   }
   if (blocks > 2 * 148 && blocks <= 5 * 148)
