@@ -546,7 +546,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);                       // page buffers, later the partials
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw + fused_base_bytes(FSTAGES));  // [16][DP] rotated queries
   bf16* kv_new = q_s + 16 * DP;                                         // [2][D] the new token's key and value
-  float* inbox = reinterpret_cast<float*>(kv_new + 2 * D);              // [splits][inbox_rows][D / splits + 2, padded to a multiple of 4]
+  float* inbox = reinterpret_cast<float*>(kv_new + 2 * D);              // [splits][inbox_rows][D + 2], used in block 0
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   KRK_TRACE_DECL
@@ -588,7 +588,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     cp_async_commit();
   };
 #pragma unroll
-  for (int i = 0; i < FSTAGES; ++i) issue(j_lo + i);  // every stage: with few pages per block all of them travel now
+  for (int i = 0; i < FSTAGES - 1; ++i) issue(j_lo + i);
   // the page that takes the new token's key and value (read here, ahead of the wait, by the block that writes them)
   const int page_new = (owns_new && rt == 0) ? table[(size_t)slot * width + j_last % width] : 0;
   // The new token's rows. Warp w takes query rows w, w + 4, ... of this tile (rows beyond G
@@ -678,6 +678,7 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
 
   for (int j = j_lo; j <= j_hi; ++j) {
     const int stage = (j - j_lo) % FSTAGES;
+    issue(j + FSTAGES - 1);
     cp_async_wait<FSTAGES - 1>();      // all but the newest FSTAGES - 1 groups: page j has landed
     __syncthreads();
     bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
@@ -702,20 +703,20 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     softmax_update<2>(s, m, l, o);
     pv_tile<2>(o, s, vs, key0, lane);
     __syncthreads();
-    issue(j + FSTAGES);                // into the stage that this iteration has finished with
   }
 
   KRK_TRACE_MARK(2)
   cp_async_wait<0>();
-  // Merge the four warps through shared memory, in warp order; then every block of the cluster
-  // takes D / splits of the head's dimensions: a block pushes that slice of its partial
-  // o[D] per row, with the row's (m, l), into the inbox of the block that owns the slice,
-  // through distributed shared memory. One cluster barrier later each block holds every
-  // split's partial of its slice and merges them in split order, so the merge and the
-  // store of the result are spread over the cluster and an inbox is a few kilobytes.
+  // Merge the four warps through shared memory, in warp order, and push the block's partial
+  // (m, l, o[D]) per row straight into block 0's inbox through distributed shared memory.
+  // One cluster barrier later block 0 holds every split's partial locally and merges them in
+  // split order; the other blocks are done, and their shared memory is free for the blocks of the
+  // kernel that follows. (The merge spread over the cluster, every block taking D / splits of the
+  // head's dimensions with inboxes of a few KB and 16-byte pushes, was measured: a step of eight
+  // sequences 2.09 -> 2.17 ms, of one 1.915 -> 1.947, because all blocks then stay to the end.)
   constexpr int RP = D + 2;
   float* red = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][RP]; the page buffers are free now
-  const int DS = D / n_splits, IW = (DS + 2 + 3) & ~3;  // an inbox row: DS values, m, l, padded to 16 bytes
+  float* inbox0 = cluster.map_shared_rank(inbox, 0);  // [splits][inbox_rows][RP] in block 0
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float* dst = red + ((size_t)warp * 16 + g + 8 * h) * RP;
@@ -727,7 +728,6 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     }
   }
   __syncthreads();
-  KRK_TRACE_MARK(3)
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block of the cluster has started
   for (int r = warp; r < q_rows; r += 4) {
     float mw[4], big = -INFINITY;
@@ -737,53 +737,44 @@ attention_decode_fused_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     float wgt[4], lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) { wgt[w] = exp2f(mw[w] - safe); lsum += wgt[w] * red[((size_t)w * 16 + r) * RP + D + 1]; }
-    const size_t at = ((size_t)split * inbox_rows + r) * IW;
-    if (DS % 4 == 0) {  // four neighbouring dimensions have one owner: one 16-byte store through the cluster's network
-      for (int d = 4 * lane; d < D; d += 128) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float* dst = inbox0 + ((size_t)split * inbox_rows + r) * RP;
+    for (int d = lane; d < D; d += 32) {
+      float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const float2* src = reinterpret_cast<const float2*>(red + ((size_t)w * 16 + r) * RP + d);
-          const float2 a = src[0], b = src[1];
-          acc.x += wgt[w] * a.x;
-          acc.y += wgt[w] * a.y;
-          acc.z += wgt[w] * b.x;
-          acc.w += wgt[w] * b.y;
-        }
-        *reinterpret_cast<float4*>(cluster.map_shared_rank(inbox, d / DS) + at + d % DS) = acc;
-      }
-    } else {
-      for (int d = lane; d < D; d += 32) {
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
-        cluster.map_shared_rank(inbox, d / DS)[at + d % DS] = acc;
-      }
+      for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * RP + d];
+      dst[d] = acc;
     }
-    if (lane < n_splits) {
-      float* dst = cluster.map_shared_rank(inbox, lane) + at;
-      dst[DS] = big;
-      dst[DS + 1] = lsum;
-    }
+    if (lane == 0) { dst[D] = big; dst[D + 1] = lsum; }
   }
   KRK_TRACE_READY
-  KRK_TRACE_MARK(4)
-  cluster.sync();  // every block's slice of every partial has arrived
-  KRK_TRACE_MARK(5)
-  for (int idx = threadIdx.x; idx < q_rows * DS; idx += THREADS) {
-    const int r = idx / DS, d = idx % DS;
-    const float* mine = inbox + (size_t)r * IW;
-    const size_t step = (size_t)inbox_rows * IW;
-    float big = -INFINITY;
-    for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, mine[s2 * step + DS]);
-    float lsum = 0.f, acc = 0.f;
-    for (int s2 = 0; s2 < n_splits; ++s2) {
-      const float w = exp2f(mine[s2 * step + DS] - big);
-      lsum += w * mine[s2 * step + DS + 1];
-      acc += w * mine[s2 * step + d];
+  cluster.sync();  // every block's partial has arrived in block 0
+  if (split == 0) {
+    for (int r = warp; r < q_rows; r += 4) {
+      const float* mine = inbox + (size_t)r * RP;
+      const size_t step = (size_t)inbox_rows * RP;
+      float big = -INFINITY;
+      for (int s2 = 0; s2 < n_splits; ++s2) big = fmaxf(big, mine[s2 * step + D]);
+      float lsum = 0.f;
+      float acc[(D + 31) / 32];
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+      for (int s2 = 0; s2 < n_splits; ++s2) {
+        const float w = exp2f(mine[s2 * step + D] - big);
+        lsum += w * mine[s2 * step + D + 1];
+#pragma unroll
+        for (int i = 0; i < (D + 31) / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) acc[i] += w * mine[s2 * step + d];
+        }
+      }
+      const float inv = 1.0f / lsum;
+      bf16* dst = out + ((size_t)seq * HQ + kh * G + rt * 16 + r) * D;
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+      }
     }
-    const float inv = 1.0f / lsum;
-    out[((size_t)seq * HQ + kh * G + rt * 16 + r) * D + split * DS + d] = __float2bfloat16_rn(acc * inv);
   }
   KRK_TRACE_END(2)
   KRK_TRACE_MARKS_OUT(3)
@@ -798,8 +789,8 @@ int launch_decode_fused(bf16* out, const bf16* qkv, int q_stride, int HQ, int HK
   const int row_tiles = (G + 15) / 16;
   const int inbox_rows = G < 16 ? G : 16;
   const size_t smem = fused_base_bytes(FSTAGES) + (size_t)(16 * DP + 2 * D) * sizeof(bf16) +
-                      (size_t)splits * inbox_rows * ((D / splits + 2 + 3) & ~3) * sizeof(float);
-  if (smem > 220 * 1024 || D % splits) return -2;
+                      (size_t)splits * inbox_rows * (D + 2) * sizeof(float);
+  if (smem > 220 * 1024) return -2;
   auto kern = attention_decode_fused_kernel<FSTAGES>;
   static size_t configured = 0;
   if (smem > configured) {

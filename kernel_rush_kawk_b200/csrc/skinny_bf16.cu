@@ -368,16 +368,13 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
            int N, int K, float eps, cudaStream_t stream) {
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
   // Between two and three blocks per SM: small blocks, but with rings as deep as three of them fit beside one
-  // another, since what bounds a block is the bytes it has in flight. With the norm prologue (one or two rows:
-  // the QKV projection of a step of one sequence) the ring is shallower, so that the blocks of the kernel that
-  // follows, the single-token attention with its 70 KB of pages, fit beside three of these and request their
-  // pages while this kernel still streams (one sequence of the 4B shape: 1.98 -> 1.95 ms a step, together with
-  // the L2 hint of the weight copies). Without the prologue (three to sixteen rows) the depth makes no
-  // difference inside a step: eight loads against eleven at eight rows, six against eight at sixteen, each
-  // within 0.3 % in alternating runs.
+  // another, since what bounds a block is the bytes it has in flight (with the norm prologue, one or two rows:
+  // fourteen loads; a step of one sequence of the 4B shape, alternating runs: 1.913 ms against 1.925 with twelve
+  // and 1.919 with ten; without the prologue the depth makes no difference inside a step: eight loads against
+  // eleven at eight rows, six against eight at sixteen, each within 0.3 %).
   if constexpr (!SWIGLU && RT == 1) {
     if (blocks > 2 * 148 && blocks <= 3 * 148)
-      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 10 : NT == 1 ? 11 : 8)>(
+      return launch_warps<4, NT, RT, SWIGLU, NORM, TOut, false, 1, (NORM ? 14 : NT == 1 ? 11 : 8)>(
           out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
   }
   if (blocks > 2 * 148 && blocks <= 5 * 148)
