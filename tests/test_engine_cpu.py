@@ -100,3 +100,53 @@ def test_generation_on_the_cpu_stand_in(folders):
         assert [s[i] for s in steps] == plain.generate_greedy(cfg, w, p, 5)
     with pytest.raises(ValueError, match="context"):
         list(engine.generate([[1] * 9000], 4))
+
+
+def test_attention_part_with_a_rotation_of_part_of_the_head_on_the_stand_in():
+    """Tables narrower than half the head rotate the first `2 * columns` elements of a head only (pairs
+    (i, i + rot/2); the norm is over the whole head). The attention part passes them through as they are;
+    here with the kernels' torch restatement, whole and in pieces, against the computation written out."""
+    from kernel_rush_kawk_b200.cache import SequenceCache
+    from kernel_rush_kawk_b200.engine.model import Runtime
+    from kernel_rush_kawk_b200.engine.step import BatchMeta, StepContext
+    from kernel_rush_kawk_b200.parts import GQAttention, RotaryTable
+
+    dtype = torch.float32
+    rt = Runtime(torch.device("cpu"), dtype, TorchOps(dtype))
+    H, HQ, HKV, D, ROT, T, EPS = 40, 4, 2, 24, 8, 70, 1e-5
+    g = torch.Generator().manual_seed(5)
+    rnd = lambda *shape: torch.randn(shape, generator=g)
+    part = GQAttention({"hidden": H, "heads": HQ, "kv_heads": HKV, "head_dim": D, "eps": EPS})
+    rope = RotaryTable({"theta": 1e4, "dim": ROT, "positions": 128})
+    rope.bind({}, rt)
+    part.set_position(rope)
+    w = {"q_proj": 0.1 * rnd(HQ * D, H), "k_proj": 0.1 * rnd(HKV * D, H), "v_proj": 0.1 * rnd(HKV * D, H),
+         "o_proj": 0.1 * rnd(H, HQ * D), "q_norm": 1.5 + 0.1 * rnd(D), "k_norm": 0.8 + 0.1 * rnd(D)}
+    part.bind(dict(w), rt)
+    h = rnd(T, H)
+    pc, ps = plain.rope_tables(ROT, 1e4, T)
+
+    def norm_rotate(x, gain):
+        y = gain * (x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + EPS))
+        y1, y2, rest = y[..., :ROT // 2], y[..., ROT // 2:ROT], y[..., ROT:]
+        c, s = pc[:, None, :], ps[:, None, :]
+        return torch.cat([y1 * c - y2 * s, y2 * c + y1 * s, rest], dim=-1)
+
+    q = norm_rotate(plain.linear(h, w["q_proj"]).view(T, HQ, D), w["q_norm"])
+    k = norm_rotate(plain.linear(h, w["k_proj"]).view(T, HKV, D), w["k_norm"])
+    v = plain.linear(h, w["v_proj"]).view(T, HKV, D)
+    want = plain.linear(plain.causal_gqa_attention(q, k, v), w["o_proj"])
+
+    for pieces in ([T], [33, 30, 1, 1, 1, 1, 1, 1, 1]):
+        cache = SequenceCache([part.cache_need()], 128, 2, 128, rt.device, dtype, step_tokens=64)
+        slot = cache.alloc()
+        got, start = [], 0
+        for n in pieces:
+            cache.reserve(slot, start + n)
+            cache.sync()
+            meta = BatchMeta(n, 1, 0, rt.device)
+            meta.fill([slot], [start], [[0] * n], [])
+            got.append(part.forward(StepContext(rt.ops, meta, cache), h[start:start + n], cache.view(0)))
+            cache.advance(slot, n)
+            start += n
+        assert_close(torch.cat(got), want, "float32", f"partial rotation on the stand-in, pieces {pieces}")
